@@ -1,0 +1,82 @@
+/*
+ * thrust_b200 -- C ABI of the B200 (sm_100a) backend for Thrust's core parallel algorithms.
+ *
+ * This is the boundary a binding generator (cgo, JNI, ctypes, a C++ header overlay) links
+ * against.  Conventions, the same for every entry point:
+ *
+ *   - All data pointers are DEVICE pointers on the current device unless a parameter name starts
+ *     with h_.  The caller owns every buffer; nothing here allocates or frees device memory.
+ *   - Scratch memory is passed in as (d_ws, ws_bytes).  Calling with d_ws == NULL performs no
+ *     work and stores the required size in *ws_bytes -- the two-phase convention of the
+ *     reference's doit_step (thrust/system/cuda/detail/copy_if.h:602-691).  With d_ws != NULL,
+ *     *ws_bytes must be at least that size, else cudaErrorInvalidValue (1) is returned.
+ *   - Work is enqueued on `stream` and the call returns without synchronising.  Counts (number
+ *     of selected items, number of runs) are written to device words the caller names and, as a
+ *     copy, into the workspace header; read them after synchronising the stream.
+ *   - The return value is a cudaError_t (0 = success).  Unsupported type combinations return
+ *     cudaErrorNotSupported (801).  Kernels bound every inter-CTA wait; a wait that ran out is
+ *     reported by tb200_workspace_status(), never by a hang.
+ *   - Element types are named by tb200_dtype codes, operators by tb200_op, predicates by
+ *     tb200_pred with two integer operands.
+ */
+#ifndef THRUST_B200_H
+#define THRUST_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* tb200_stream_t; /* == cudaStream_t */
+
+enum tb200_dtype {
+  TB200_I8 = 0, TB200_U8 = 1, TB200_I16 = 2, TB200_U16 = 3, TB200_I32 = 4,
+  TB200_U32 = 5, TB200_I64 = 6, TB200_U64 = 7, TB200_F32 = 8, TB200_F64 = 9
+};
+enum tb200_op { TB200_PLUS = 0, TB200_MIN = 1, TB200_MAX = 2 };
+/* MOD_EQ: x % a == b    LT: x < a    GE: x >= a    NE: x != a */
+enum tb200_pred { TB200_PRED_MOD_EQ = 0, TB200_PRED_LT = 1, TB200_PRED_GE = 2, TB200_PRED_NE = 3 };
+
+/* Library version (major * 10000 + minor * 100 + patch) and the SM architecture it was built for. */
+int tb200_version(void);
+int tb200_sm_arch(void);
+
+/* Reads the status word of a workspace after the work that used it has completed: synchronises
+ * `stream`, copies 4 bytes back.  *h_status: 0 = ok, 1 = a look-back wait ran out (results of
+ * that call are invalid).  Stands in for the reference's post-launch error check,
+ * cuda_cub::throw_on_error (thrust/system/cuda/detail/util.h:180-243). */
+int tb200_workspace_status(const void* d_ws, tb200_stream_t stream, unsigned* h_status);
+
+/* thrust::reduce(first, last, init, op) -- thrust/system/cuda/detail/reduce.h:1015-1067
+ * (cuda_cub::reduce_n).  Accumulates in acc_t, the type of *h_init; each input element is
+ * converted to acc_t first.  Result: one acc_t at d_out.  n == 0 stores init.
+ * (in_t, acc_t): equal 4/8-byte types, or widening within a family: I8/I16/I32 -> I32/I64,
+ * U8/U16/U32 -> U32/U64, F32 -> F64. */
+int tb200_reduce(const void* d_in, size_t n, int in_t, int acc_t, int op, const void* h_init,
+                 void* d_out, void* d_ws, size_t* ws_bytes, tb200_stream_t stream);
+
+/* thrust::inclusive_scan / thrust::exclusive_scan -- thrust/system/cuda/detail/scan.h:215-361
+ * (cuda_cub::inclusive_scan_n, exclusive_scan_n).  Element type t (I32 U32 I64 U64 F32 F64) for
+ * input, output and accumulator.  d_in == d_out is allowed. */
+int tb200_inclusive_scan(const void* d_in, void* d_out, size_t n, int t, int op, void* d_ws,
+                         size_t* ws_bytes, tb200_stream_t stream);
+int tb200_exclusive_scan(const void* d_in, void* d_out, size_t n, int t, int op,
+                         const void* h_init, void* d_ws, size_t* ws_bytes, tb200_stream_t stream);
+
+/* thrust::sort / stable_sort / sort_by_key / stable_sort_by_key with thrust::less (descending=0)
+ * or thrust::greater (descending=1) on arithmetic keys -- thrust/system/cuda/detail/sort.h:
+ * 1621-1754, radix path :1438-1508.  Stable.  Sorts d_keys (and d_vals) in place; d_keys_alt /
+ * d_vals_alt are caller-provided buffers of the same size that play the part of the reference's
+ * double buffer (sort.h:1465-1484).  key_t: I32 U32 F32 I64 U64 F64.  val_bytes: 0 (keys only),
+ * 4 or 8.  Only key bits [begin_bit, end_bit) are compared (multiples of 8; pass 0 and
+ * 8*sizeof(key) for a full sort).  n < 2^31, as in the reference (sort.h:1346). */
+int tb200_sort_by_key(void* d_keys, void* d_keys_alt, void* d_vals, void* d_vals_alt, size_t n,
+                      int key_t, int val_bytes, int descending, int begin_bit, int end_bit,
+                      void* d_ws, size_t* ws_bytes, tb200_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,321 @@
+// Shared device/host helpers for the B200 (sm_100a) parallel-algorithm kernels.
+//
+// Everything here is header-only so that the same kernel templates serve two callers: the
+// precompiled C-ABI library (fixed element types and functors) and the Thrust header overlay
+// (the user's iterator and functor types).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stddef.h>
+#include <type_traits>
+
+namespace tb200 {
+
+constexpr int WARP_THREADS = 32;
+constexpr unsigned FULL_MASK = 0xffffffffu;
+
+// Error codes a kernel may leave in the workspace status word (see ws_header).
+enum : unsigned { ERR_NONE = 0, ERR_LOOKBACK_TIMEOUT = 1 };
+
+// Number of polls of a predecessor's status word before a look-back gives up, records
+// ERR_LOOKBACK_TIMEOUT and carries on with whatever it has.  Polls past the first few sleep
+// ~100 ns, so the bound is of the order of a second: far beyond any legitimate wait, short
+// enough that a broken launch returns instead of hanging the device.
+constexpr unsigned SPIN_LIMIT = 1u << 23;
+
+// First 256 bytes of every workspace.
+struct ws_header {
+  unsigned error;          // ERR_* (sticky until the next call clears it)
+  unsigned ticket;         // dynamic tile counter / last-block counter
+  unsigned long long count;  // number of selected items / runs / ... written by the kernel
+  unsigned ticket2;
+  unsigned flags;
+  unsigned long long aux[29];
+};
+static_assert(sizeof(ws_header) == 256, "workspace header is 256 bytes");
+
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+struct device_info { int sm_count; int max_smem_optin; };
+inline const device_info& current_device_info() {
+  static thread_local device_info cache[64];
+  static thread_local bool have[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (!have[dev]) {
+    cudaDeviceGetAttribute(&cache[dev].sm_count, cudaDevAttrMultiProcessorCount, dev);
+    cudaDeviceGetAttribute(&cache[dev].max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    have[dev] = true;
+  }
+  return cache[dev];
+}
+
+// ---------------------------------------------------------------- functors
+struct plus_op { template <class T> __host__ __device__ T operator()(const T& a, const T& b) const { return a + b; } };
+struct min_op { template <class T> __host__ __device__ T operator()(const T& a, const T& b) const { return b < a ? b : a; } };
+struct max_op { template <class T> __host__ __device__ T operator()(const T& a, const T& b) const { return a < b ? b : a; } };
+struct equal_op { template <class T> __host__ __device__ bool operator()(const T& a, const T& b) const { return a == b; } };
+struct less_op { template <class T> __host__ __device__ bool operator()(const T& a, const T& b) const { return a < b; } };
+struct greater_op { template <class T> __host__ __device__ bool operator()(const T& a, const T& b) const { return b < a; } };
+
+// Predicate of the C ABI: kind 0: x % a == b, 1: x < a, 2: x >= a, 3: x != a.
+struct abi_pred {
+  int kind; long long a, b;
+  template <class T> __host__ __device__ bool operator()(const T& x) const {
+    switch (kind) {
+      case 0: return (long long)x % a == b;
+      case 1: return x < (T)a;
+      case 2: return x >= (T)a;
+      default: return x != (T)a;
+    }
+  }
+};
+
+// A value that may be absent: lets scans and reductions run on operators without an identity.
+template <class T> struct opt {
+  T v; bool has;
+  template <class Op> __device__ __forceinline__ void append(const T& x, Op op) {  // this = this (+) x
+    v = has ? op(v, x) : x; has = true;
+  }
+  template <class Op> __device__ __forceinline__ void prepend(const opt<T>& left, Op op) {  // this = left (+) this
+    if (left.has) { v = has ? op(left.v, v) : left.v; has = true; }
+  }
+};
+
+// ---------------------------------------------------------------- shuffles of any small POD
+template <class T> __device__ __forceinline__ T shfl_generic(const T& x, int src_lane, int mode, int arg) {
+  // mode 0: idx, 1: up, 2: down, 3: xor
+  constexpr int W = (sizeof(T) + 3) / 4;
+  union { T t; unsigned w[W]; } in, out;
+  in.t = x;
+#pragma unroll
+  for (int i = 0; i < W; ++i) {
+    if (mode == 0) out.w[i] = __shfl_sync(FULL_MASK, in.w[i], src_lane);
+    else if (mode == 1) out.w[i] = __shfl_up_sync(FULL_MASK, in.w[i], arg);
+    else if (mode == 2) out.w[i] = __shfl_down_sync(FULL_MASK, in.w[i], arg);
+    else out.w[i] = __shfl_xor_sync(FULL_MASK, in.w[i], arg);
+  }
+  return out.t;
+}
+template <class T> __device__ __forceinline__ T shfl_idx(const T& x, int lane) { return shfl_generic(x, lane, 0, 0); }
+template <class T> __device__ __forceinline__ T shfl_up(const T& x, int d) { return shfl_generic(x, 0, 1, d); }
+template <class T> __device__ __forceinline__ T shfl_down(const T& x, int d) { return shfl_generic(x, 0, 2, d); }
+
+__device__ __forceinline__ int lane_id() { return threadIdx.x & 31; }
+
+// Inclusive scan across the lanes of a warp; lane 0 keeps its own value.
+template <class T, class Op> __device__ __forceinline__ T warp_inclusive_scan(T x, Op op) {
+  const int lane = lane_id();
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    T y = shfl_up(x, d);
+    if (lane >= d) x = op(y, x);
+  }
+  return x;
+}
+
+// Reduction across a warp of values that may be absent; operands keep lane order (lower lane on
+// the left), so the operator need not commute.  Result valid in lane 0.
+template <class T, class Op> __device__ __forceinline__ opt<T> warp_reduce_opt(opt<T> x, Op op) {
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    T y = shfl_down(x.v, d);
+    int yh = __shfl_down_sync(FULL_MASK, (int)x.has, d);
+    if (lane_id() + d < 32 && yh) { x.v = x.has ? op(x.v, y) : y; x.has = true; }
+  }
+  return x;
+}
+
+// ---------------------------------------------------------------- memory access
+// Streaming (evict-first) 16-byte load/store: the data is touched once.
+struct __align__(16) vec16 { unsigned x, y, z, w; };
+__device__ __forceinline__ vec16 load_stream16(const void* p) {
+  vec16 v;
+  asm volatile("ld.global.cs.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void store_stream16(void* p, const vec16& v) {
+  asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+__device__ __forceinline__ unsigned long long ld_relaxed_u64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_relaxed_u64(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_u32(unsigned* p, unsigned v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_relaxed_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_relaxed_u32(unsigned* p, unsigned v) {
+  asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ void record_error(unsigned* err, unsigned code) { atomicCAS(err, ERR_NONE, code); }
+
+__device__ __forceinline__ void backoff(unsigned iter) { if (iter > 8) __nanosleep(iter > 64 ? 200 : 40); }
+
+inline bool is_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// ---------------------------------------------------------------- decoupled look-back state
+// One descriptor per tile.  status: 0 = nothing yet, 1 = tile aggregate available,
+// 2 = inclusive prefix (everything up to and including this tile) available.
+enum : unsigned { TILE_INVALID = 0, TILE_AGGREGATE = 1, TILE_INCLUSIVE = 2 };
+
+// 4-byte values travel with their status in one 64-bit word (one relaxed store, no fence);
+// anything else is written first and published by a release store of the status.
+template <class T, bool PACKED = (sizeof(T) == 4)> struct tile_state;
+
+template <class T> struct tile_state<T, true> {
+  unsigned long long* words;
+  static size_t bytes(size_t tiles) { return align_up(tiles * 8, 256); }
+  void bind(void* p, size_t) { words = static_cast<unsigned long long*>(p); }
+  __device__ __forceinline__ void publish(size_t tile, unsigned status, const T& v) const {
+    union { T t; unsigned u; } c; c.t = v;
+    st_relaxed_u64(words + tile, ((unsigned long long)status << 32) | c.u);
+  }
+  __device__ __forceinline__ unsigned poll(size_t tile, T& v) const {
+    unsigned long long w = ld_relaxed_u64(words + tile);
+    union { T t; unsigned u; } c; c.u = (unsigned)w; v = c.t;
+    return (unsigned)(w >> 32);
+  }
+};
+
+template <class T> struct tile_state<T, false> {
+  unsigned* status; T* agg; T* inc;
+  static size_t slot() { return (sizeof(T) + 15) / 16 * 16; }
+  static size_t bytes(size_t tiles) { return align_up(tiles * 4, 256) + 2 * align_up(tiles * sizeof(T), 256); }
+  void bind(void* p, size_t tiles) {
+    char* c = static_cast<char*>(p);
+    status = reinterpret_cast<unsigned*>(c); c += align_up(tiles * 4, 256);
+    agg = reinterpret_cast<T*>(c); c += align_up(tiles * sizeof(T), 256);
+    inc = reinterpret_cast<T*>(c);
+  }
+  __device__ __forceinline__ void publish(size_t tile, unsigned st, const T& v) const {
+    (st == TILE_AGGREGATE ? agg : inc)[tile] = v;
+    st_release_u32(status + tile, st);
+  }
+  __device__ __forceinline__ unsigned poll(size_t tile, T& v) const {
+    unsigned st = ld_acquire_u32(status + tile);
+    if (st == TILE_AGGREGATE) v = agg[tile];
+    else if (st == TILE_INCLUSIVE) v = inc[tile];
+    return st;
+  }
+};
+
+// Warp-wide decoupled look-back.  Called by all 32 lanes of one warp of tile `tile` (> 0) after
+// that tile's own aggregate has been published.  Returns (in every lane) the combination of all
+// preceding tiles, oldest on the left.  Tile 0 always publishes TILE_INCLUSIVE, so the walk ends
+// there at the latest.  Waits are bounded by SPIN_LIMIT.
+template <class T, class Op, class State>
+__device__ __forceinline__ T lookback_prefix(const State& ts, size_t tile, Op op, unsigned* err) {
+  const int lane = lane_id();
+  opt<T> running; running.has = false;
+  long long window_end = (long long)tile - 1;
+  while (true) {
+    long long idx = window_end - lane;
+    opt<T> mine; mine.has = false;
+    unsigned st = TILE_INCLUSIVE;  // lanes before tile 0 read as "stop", contributing nothing
+    if (idx >= 0) {
+      unsigned iter = 0;
+      while ((st = ts.poll((size_t)idx, mine.v)) == TILE_INVALID) {
+        if (++iter > SPIN_LIMIT) { record_error(err, ERR_LOOKBACK_TIMEOUT); st = TILE_INCLUSIVE; mine.has = false; break; }
+        backoff(iter);
+      }
+      if (iter <= SPIN_LIMIT) mine.has = true;
+    }
+    unsigned stop_mask = __ballot_sync(FULL_MASK, st == TILE_INCLUSIVE);
+    int first_stop = stop_mask ? (__ffs(stop_mask) - 1) : 32;
+    if (lane > first_stop) mine.has = false;
+    // combine lanes: higher lane = older tile = left operand
+    opt<T> w = mine;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      T y = shfl_down(w.v, d);
+      int yh = __shfl_down_sync(FULL_MASK, (int)w.has, d);
+      if (lane + d < 32 && yh) { w.v = w.has ? op(y, w.v) : y; w.has = true; }
+    }
+    w.v = shfl_idx(w.v, 0);
+    w.has = __shfl_sync(FULL_MASK, (int)w.has, 0);
+    running.prepend(w, op);
+    if (stop_mask) break;
+    window_end -= 32;
+  }
+  return running.v;
+}
+
+// ---------------------------------------------------------------- tile-wide exclusive prefix
+// The common core of scan, stream compaction and reduce-by-key.  A tile is BLOCK threads; every
+// thread holds VPT "vectors" laid out lane-interleaved inside its warp's chunk: tile order is
+// (warp, v, lane).  Given each vector's total, computes for each vector the combination of
+// everything that precedes it -- earlier lanes of the row, earlier rows, earlier warps, earlier
+// tiles (decoupled look-back) and the optional initial value -- without needing an identity.
+template <class T, int NWARPS> struct tile_prefix_smem {
+  T warp_total[NWARPS];
+  T prefix;          // combination of all preceding tiles (and init)
+  T inclusive;       // prefix (+) this tile's aggregate
+  bool has_prefix;
+};
+
+template <class T, class Op, int VPT, int NWARPS, class State>
+__device__ __forceinline__ void tile_exclusive_prefix(const T (&vec_total)[VPT], opt<T> (&pre)[VPT], size_t tile, const T& init,
+                                                      bool has_init, Op op, const State& ts, unsigned* err,
+                                                      tile_prefix_smem<T, NWARPS>& sm) {
+  const int lane = lane_id(), warp = threadIdx.x >> 5;
+  T rowacc = vec_total[0];
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    T incl = warp_inclusive_scan(vec_total[v], op);
+    T rowtotal = shfl_idx(incl, 31);
+    T lanepref = shfl_up(incl, 1);
+    pre[v].has = false;
+    if (v > 0) { pre[v].v = rowacc; pre[v].has = true; }
+    if (lane > 0) pre[v].append(lanepref, op);
+    rowacc = v > 0 ? op(rowacc, rowtotal) : rowtotal;
+  }
+  if (lane == 0) sm.warp_total[warp] = rowacc;
+  __syncthreads();
+  opt<T> wp; wp.has = false;
+  for (int w = 0; w < warp; ++w) wp.append(sm.warp_total[w], op);
+  if (warp == 0) {
+    T agg = sm.warp_total[0];
+#pragma unroll
+    for (int w = 1; w < NWARPS; ++w) agg = op(agg, sm.warp_total[w]);
+    if (tile == 0) {
+      T inc = has_init ? op(init, agg) : agg;
+      if (lane == 0) {
+        ts.publish(0, TILE_INCLUSIVE, inc);
+        sm.prefix = init; sm.has_prefix = has_init; sm.inclusive = inc;
+      }
+    } else {
+      if (lane == 0) ts.publish(tile, TILE_AGGREGATE, agg);
+      __syncwarp();
+      T p = lookback_prefix<T>(ts, tile, op, err);
+      if (lane == 0) {
+        T inc = op(p, agg);
+        ts.publish(tile, TILE_INCLUSIVE, inc);
+        sm.prefix = p; sm.has_prefix = true; sm.inclusive = inc;
+      }
+    }
+  }
+  __syncthreads();
+  opt<T> tp; tp.v = sm.prefix; tp.has = sm.has_prefix;
+  wp.prepend(tp, op);
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) pre[v].prepend(wp, op);
+}
+
+}  // namespace tb200

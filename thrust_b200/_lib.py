@@ -1,0 +1,44 @@
+"""Loads libthrust_b200.so and declares the C-ABI prototypes (include/thrust_b200.h).
+
+There is no fallback: if the library is missing or a symbol is absent this raises, so that a
+caller can never silently run anything but the sm_100a kernels.
+"""
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libthrust_b200.so")
+
+_vp, _sz, _i = C.c_void_p, C.c_size_t, C.c_int
+_szp = C.POINTER(C.c_size_t)
+
+# name -> argtypes; every function returns int (cudaError_t)
+PROTOTYPES = {
+    "tb200_version": [],
+    "tb200_sm_arch": [],
+    "tb200_workspace_status": [_vp, _vp, C.POINTER(C.c_uint)],
+    "tb200_reduce": [_vp, _sz, _i, _i, _i, _vp, _vp, _vp, _szp, _vp],
+    "tb200_inclusive_scan": [_vp, _vp, _sz, _i, _i, _vp, _szp, _vp],
+    "tb200_exclusive_scan": [_vp, _vp, _sz, _i, _i, _vp, _vp, _szp, _vp],
+    "tb200_sort_by_key": [_vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _vp, _szp, _vp],
+}
+
+_lib = None
+
+
+def load():
+    """Returns the ctypes handle, loading the library on first use."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.isfile(LIB_PATH):
+        raise RuntimeError(
+            "thrust_b200: %s is missing -- build it with `python -m thrust_b200.build`; "
+            "there is no CPU or library fallback" % LIB_PATH)
+    lib = C.CDLL(LIB_PATH)
+    for name, args in PROTOTYPES.items():
+        fn = getattr(lib, name)  # AttributeError if the symbol is not exported
+        fn.argtypes = args
+        fn.restype = C.c_int
+    _lib = lib
+    return lib

@@ -1,0 +1,162 @@
+"""Host-side mirror of the Thrust algorithms on the hot path, over the C ABI.
+
+Function names, argument meaning and return conventions follow the reference's CUDA backend
+(thrust/system/cuda/detail/{reduce,scan,sort,copy_if,partition,unique,reduce_by_key,merge}.h):
+synchronous on return, results that are counts come back as Python ints, "end iterators" come
+back as the output tensor sliced to its logical length.  Inputs are CUDA torch tensors; torch is
+used only to own device memory and to name the stream.  Every call goes through
+libthrust_b200.so; there is no fallback path.
+"""
+import ctypes as C
+
+import numpy as np
+import torch
+
+from . import _lib
+
+DTYPE_CODE = {
+    torch.int8: 0, torch.uint8: 1, torch.int16: 2, torch.uint16: 3, torch.int32: 4,
+    torch.uint32: 5, torch.int64: 6, torch.uint64: 7, torch.float32: 8, torch.float64: 9,
+}
+NP_OF = {
+    torch.int8: np.int8, torch.uint8: np.uint8, torch.int16: np.int16, torch.uint16: np.uint16,
+    torch.int32: np.int32, torch.uint32: np.uint32, torch.int64: np.int64, torch.uint64: np.uint64,
+    torch.float32: np.float32, torch.float64: np.float64,
+}
+TORCH_OF = {np.dtype(v): k for k, v in NP_OF.items()}
+OPS = {"plus": 0, "min": 1, "max": 2}
+PREDS = {"mod_eq": 0, "lt": 1, "ge": 2, "ne": 3}
+
+
+class Tb200Error(RuntimeError):
+    """A C-ABI call returned a CUDA error, or a kernel reported a failed wait."""
+
+
+def _check(rc, what):
+    if rc != 0:
+        raise Tb200Error("%s failed with cudaError %d" % (what, rc))
+
+
+def _ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and (not t.is_cuda or not t.is_contiguous()):
+            raise ValueError("thrust_b200 operates on contiguous CUDA tensors")
+
+
+class _Workspaces:
+    """Scratch buffers cached per (device, stream, call site) and grown on demand, standing in for
+    the reference's per-call temporary_array (thrust/system/cuda/detail/reduce.h:959)."""
+
+    def __init__(self):
+        self._bufs = {}
+
+    def get(self, tag, nbytes):
+        key = (torch.cuda.current_device(), torch.cuda.current_stream().cuda_stream, tag)
+        buf = self._bufs.get(key)
+        if buf is None or buf.numel() < nbytes:
+            buf = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device="cuda")
+            self._bufs[key] = buf
+        return buf
+
+    def clear(self):
+        self._bufs.clear()
+
+
+workspaces = _Workspaces()
+
+
+def _call_with_ws(tag, fn, *args):
+    """fn(*args, d_ws, &ws_bytes, stream): size query, then the real call.  Returns the workspace."""
+    lib_fn = getattr(_lib.load(), fn)
+    need = C.c_size_t(0)
+    _check(lib_fn(*args, None, C.byref(need), _stream()), fn + " (size query)")
+    ws = workspaces.get(tag, need.value)
+    have = C.c_size_t(ws.numel())
+    _check(lib_fn(*args, _ptr(ws), C.byref(have), _stream()), fn)
+    return ws
+
+
+def _sync_and_check(ws, what):
+    status = C.c_uint(0)
+    _check(_lib.load().tb200_workspace_status(_ptr(ws), _stream(), C.byref(status)), what + " (status)")
+    if status.value != 0:
+        raise Tb200Error("%s: device reported status %d (an inter-CTA wait ran out)" % (what, status.value))
+
+
+# ------------------------------------------------------------------------------------- reduce
+def reduce(x, init=None, op="plus", acc_dtype=None):
+    """thrust::reduce(first, last, init, op): returns init (+) x[0] (+) ... as a numpy scalar of the
+    accumulator type (the type of `init`; default: x's type and 0, as in reduce.h:1057-1067)."""
+    _require_cuda(x)
+    if acc_dtype is None:
+        acc_dtype = x.dtype if init is None or not isinstance(init, np.generic) else TORCH_OF[np.dtype(init.dtype)]
+    h_init = np.asarray(0 if init is None else init, dtype=NP_OF[acc_dtype])
+    out = torch.empty(1, dtype=acc_dtype, device=x.device)
+    ws = _call_with_ws("reduce", "tb200_reduce", _ptr(x), x.numel(), DTYPE_CODE[x.dtype], DTYPE_CODE[acc_dtype],
+                       OPS[op], C.c_void_p(h_init.ctypes.data), _ptr(out))
+    _sync_and_check(ws, "reduce")
+    return out.cpu().numpy().view(NP_OF[acc_dtype])[0]
+
+
+# ------------------------------------------------------------------------------------- scan
+def inclusive_scan(x, out=None, op="plus"):
+    """thrust::inclusive_scan(first, last, result, op); out may be x (in place).  Returns out."""
+    _require_cuda(x, out)
+    out = torch.empty_like(x) if out is None else out
+    ws = _call_with_ws("scan", "tb200_inclusive_scan", _ptr(x), _ptr(out), x.numel(), DTYPE_CODE[x.dtype], OPS[op])
+    _sync_and_check(ws, "inclusive_scan")
+    return out
+
+
+def exclusive_scan(x, init=0, out=None, op="plus"):
+    """thrust::exclusive_scan(first, last, result, init, op)."""
+    _require_cuda(x, out)
+    out = torch.empty_like(x) if out is None else out
+    h_init = np.asarray(init, dtype=NP_OF[x.dtype])
+    ws = _call_with_ws("scan", "tb200_exclusive_scan", _ptr(x), _ptr(out), x.numel(), DTYPE_CODE[x.dtype], OPS[op],
+                       C.c_void_p(h_init.ctypes.data))
+    _sync_and_check(ws, "exclusive_scan")
+    return out
+
+
+# ------------------------------------------------------------------------------------- sort
+def _sort_impl(keys, vals, descending, begin_bit, end_bit, sync=True):
+    _require_cuda(keys, vals)
+    if vals is not None and vals.numel() != keys.numel():
+        raise ValueError("keys and values differ in length")
+    n = keys.numel()
+    vb = 0 if vals is None else vals.element_size()
+    kalt = workspaces.get("sort_keys_alt", n * keys.element_size())
+    valt = None if vals is None else workspaces.get("sort_vals_alt", n * vb)
+    end_bit = 8 * keys.element_size() if end_bit is None else end_bit
+    ws = _call_with_ws("sort", "tb200_sort_by_key", _ptr(keys), _ptr(kalt), _ptr(vals), _ptr(valt), n,
+                       DTYPE_CODE[keys.dtype], vb, int(descending), begin_bit, end_bit)
+    if sync:
+        _sync_and_check(ws, "sort")
+
+
+def sort(keys, descending=False):
+    """thrust::sort / thrust::stable_sort(first, last[, greater]) in place."""
+    _sort_impl(keys, None, descending, 0, None)
+    return keys
+
+
+stable_sort = sort
+
+
+def sort_by_key(keys, vals, descending=False, begin_bit=0, end_bit=None):
+    """thrust::sort_by_key / stable_sort_by_key(keys_first, keys_last, values_first[, greater]) in
+    place; stable."""
+    _sort_impl(keys, vals, descending, begin_bit, end_bit)
+    return keys, vals
+
+
+stable_sort_by_key = sort_by_key
