@@ -7,7 +7,7 @@
 //   2. radix_scan_hist_kernel exclusive-scans each histogram into bucket bases and marks a digit
 //                             place as skippable when one bucket holds every key;
 //   3. onesweep_kernel        once per non-skipped digit place: a tile of keys is ranked inside
-//                             the CTA (warp match + per-warp counters), the tile's per-digit
+//                             the CTA (warp ballots + per-warp counters), the tile's per-digit
 //                             counts are chained to the preceding tiles by decoupled look-back
 //                             (one thread per digit), and keys then values are staged through
 //                             shared memory so that each bucket's run is written contiguously;
@@ -27,7 +27,7 @@ constexpr int RADIX_BITS = 8;
 constexpr int RADIX_BINS = 256;
 constexpr int RADIX_MAX_PASSES = 8;
 constexpr int ONESWEEP_BLOCK = 512;
-constexpr int HIST_BLOCK = 512;
+constexpr int HIST_BLOCK = 1024;
 
 enum key_kind : int { KEY_UNSIGNED = 0, KEY_SIGNED = 1, KEY_FLOAT = 2 };
 
@@ -35,14 +35,22 @@ struct key_coding {
   int kind; int descending;
 };
 
-template <class UK> __device__ __forceinline__ UK encode_key(UK k, key_coding c) {
+// Digit `shift / 8` of the key's order-preserving unsigned code.  For integer keys the code
+// differs from the raw bits by a constant, so the digit is the raw byte XOR `dmask` (the matching
+// byte of that constant); float keys first flip all bits of negative values.
+template <class UK> __host__ __device__ __forceinline__ unsigned digit_mask(key_coding c, int shift) {
   constexpr int B = 8 * sizeof(UK);
-  const UK sign = (UK)1 << (B - 1);
-  UK mask = 0;
-  if (c.kind == KEY_SIGNED) mask = sign;
-  else if (c.kind == KEY_FLOAT) mask = (k & sign) ? (UK)~(UK)0 : sign;
-  k ^= mask;
-  return c.descending ? (UK)~k : k;
+  UK m = c.descending ? (UK)~(UK)0 : (UK)0;
+  if (c.kind != KEY_UNSIGNED) m ^= (UK)1 << (B - 1);
+  return (unsigned)(m >> shift) & 0xffu;
+}
+template <bool IS_FLOAT, class UK> __device__ __forceinline__ unsigned key_digit(UK k, int shift, unsigned dmask) {
+  constexpr int B = 8 * sizeof(UK);
+  if (IS_FLOAT) {
+    using SK = typename std::make_signed<UK>::type;
+    k ^= (UK)((SK)k >> (B - 1)) & (UK)~((UK)1 << (B - 1));   // negative: flip the non-sign bits too
+  }
+  return ((unsigned)(k >> shift) & 0xffu) ^ dmask;
 }
 
 // Control block in the workspace, after ws_header.
@@ -54,44 +62,67 @@ struct radix_ctrl {
 };
 
 // ---------------------------------------------------------------- 1. histograms of all digit places
-template <class UK>
+// One CTA per SM.  Shared memory holds, for every digit place, COPIES interleaved copies of the
+// 256 bins; lane l only ever touches copy l % COPIES, so with 32 copies a warp's atomics never
+// share a bank and a degenerate digit (every key equal) costs no more than a uniform one.
+template <class UK> struct hist_tuning { static constexpr int COPIES = sizeof(UK) <= 4 ? 32 : 16; };
+
+template <class UK, bool IS_FLOAT>
 __global__ void __launch_bounds__(HIST_BLOCK)
 radix_hist_kernel(const UK* keys, size_t n, key_coding coding, int first_pass, int num_passes, radix_ctrl* ctrl) {
   constexpr int NP = sizeof(UK);
-  __shared__ unsigned bins[NP][RADIX_BINS];
-  for (int i = threadIdx.x; i < NP * RADIX_BINS; i += HIST_BLOCK) (&bins[0][0])[i] = 0;
+  constexpr int COPIES = hist_tuning<UK>::COPIES;
+  constexpr int VEC = 16 / sizeof(UK);
+  extern __shared__ __align__(16) unsigned hist_bins[];   // [NP][256][COPIES]
+  for (int i = threadIdx.x; i < NP * RADIX_BINS * COPIES; i += HIST_BLOCK) hist_bins[i] = 0;
   __syncthreads();
-  // thread-local run compression: a digit place where consecutive keys agree (for example the
-  // all-zero high bytes of narrow keys) costs one shared-memory atomic per run, not per key
-  unsigned last[NP]; unsigned run[NP];
+  const int col = lane_id() & (COPIES - 1);
+  unsigned dmask[NP];
 #pragma unroll
-  for (int p = 0; p < NP; ++p) { last[p] = 0; run[p] = 0; }
-  const size_t stride = (size_t)gridDim.x * HIST_BLOCK;
-  constexpr int U = 4;
-  size_t i = (size_t)blockIdx.x * HIST_BLOCK + threadIdx.x;
+  for (int p = 0; p < NP; ++p) dmask[p] = digit_mask<UK>(coding, p * RADIX_BITS);
   auto account = [&](UK k) {
-    UK e = encode_key(k, coding);
 #pragma unroll
     for (int p = 0; p < NP; ++p) {
-      unsigned d = (unsigned)(e >> (p * RADIX_BITS)) & (RADIX_BINS - 1);
-      if (d == last[p]) ++run[p];
-      else { if (run[p]) atomicAdd(&bins[p][last[p]], run[p]); last[p] = d; run[p] = 1; }
+      unsigned d = key_digit<IS_FLOAT>(k, p * RADIX_BITS, dmask[p]);
+      atomicAdd(&hist_bins[(p * RADIX_BINS + d) * COPIES + col], 1u);
     }
   };
-  for (; i + (U - 1) * stride < n; i += U * stride) {
-    UK k[U];
+  // 16-byte loads over the aligned body; the ragged head and tail one key at a time
+  const uintptr_t addr = reinterpret_cast<uintptr_t>(keys);
+  size_t head = ((16 - (addr & 15)) & 15) / sizeof(UK);
+  if (head > n) head = n;
+  const size_t nvec = (n - head) / VEC;
+  const vec16* vkeys = reinterpret_cast<const vec16*>(keys + head);
+  const size_t gtid = (size_t)blockIdx.x * HIST_BLOCK + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * HIST_BLOCK;
+  constexpr int U = 4;
+  size_t v = gtid;
+  for (; v + (U - 1) * stride < nvec; v += U * stride) {
+    vec16 r[U];
 #pragma unroll
-    for (int u = 0; u < U; ++u) k[u] = __ldcs(keys + i + u * stride);
+    for (int u = 0; u < U; ++u) r[u] = load_stream16(vkeys + v + u * stride);
 #pragma unroll
-    for (int u = 0; u < U; ++u) account(k[u]);
+    for (int u = 0; u < U; ++u) {
+      const UK* e = reinterpret_cast<const UK*>(&r[u]);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) account(e[k]);
+    }
   }
-  for (; i < n; i += stride) account(__ldcs(keys + i));
+  for (; v < nvec; v += stride) {
+    vec16 r = load_stream16(vkeys + v);
+    const UK* e = reinterpret_cast<const UK*>(&r);
 #pragma unroll
-  for (int p = 0; p < NP; ++p) if (run[p]) atomicAdd(&bins[p][last[p]], run[p]);
+    for (int k = 0; k < VEC; ++k) account(e[k]);
+  }
+  if (gtid < head) account(keys[gtid]);
+  const size_t tail0 = head + nvec * VEC;
+  if (tail0 + gtid < n) account(keys[tail0 + gtid]);
   __syncthreads();
   for (int j = threadIdx.x; j < NP * RADIX_BINS; j += HIST_BLOCK) {
-    int p = j / RADIX_BINS;
-    unsigned c = (&bins[0][0])[j];
+    const int p = j / RADIX_BINS;
+    unsigned c = 0;
+#pragma unroll
+    for (int q = 0; q < COPIES; ++q) c += hist_bins[j * COPIES + ((q + threadIdx.x) & (COPIES - 1))];
     if (c && p >= first_pass && p < first_pass + num_passes) atomicAdd(&ctrl->hist[p][j % RADIX_BINS], (unsigned long long)c);
   }
 }
@@ -117,81 +148,58 @@ radix_scan_hist_kernel(radix_ctrl* ctrl, size_t n, int first_pass) {
 
 // ---------------------------------------------------------------- 3. one digit place
 template <int KB, int VB> struct onesweep_tuning {
-  // items per thread so that one tile's staging (keys + values) stays near 80 KB
-  static constexpr int IPT = (KB + VB) <= 4 ? 22 : (KB + VB) <= 8 ? 18 : (KB + VB) <= 12 ? 13 : 10;
+  // items per thread; two 512-thread CTAs per SM (64 registers per thread, ~80 KB of staging each)
+  static constexpr int IPT = KB <= 4 ? (VB == 0 ? 18 : VB <= 4 ? 16 : 12) : (VB == 0 ? 12 : VB <= 4 ? 10 : 8);
 };
 
-template <class UK, class UV, bool HAS_V, class LB, int IPT>
-__global__ void __launch_bounds__(ONESWEEP_BLOCK)
-onesweep_kernel(UK* buf_a, UK* buf_b, UV* val_a, UV* val_b, unsigned n, key_coding coding, int pass, int first_pass,
-                radix_ctrl* ctrl, LB* lookback, ws_header* hdr) {
+template <class UK, class UV, bool HAS_V, bool IS_FLOAT, class LB, int IPT, bool FULL>
+__device__ __forceinline__ void onesweep_tile(const UK* __restrict__ src, UK* __restrict__ dst, const UV* __restrict__ vsrc,
+                                              UV* __restrict__ vdst, unsigned n, unsigned tile, int shift, unsigned dmask,
+                                              const unsigned long long* bin_base, LB* lookback, unsigned* err,
+                                              unsigned* warp_hist, unsigned* s_goff, unsigned* s_scan, UK* stage_k, UV* stage_v) {
   constexpr int NWARPS = ONESWEEP_BLOCK / 32;
   constexpr int TILE = ONESWEEP_BLOCK * IPT;
   constexpr int WCHUNK = 32 * IPT;
   constexpr int LB_BITS = 8 * sizeof(LB) - 2;
   constexpr LB LB_MASK = ((LB)1 << LB_BITS) - 1;
-
-  if (ctrl->skip[pass]) return;
-  int flips = 0;
-  for (int q = first_pass; q < pass; ++q) flips += ctrl->skip[q] ? 0 : 1;
-  const UK* src = (flips & 1) ? buf_b : buf_a;
-  UK* dst = (flips & 1) ? buf_a : buf_b;
-  const UV* vsrc = (flips & 1) ? val_b : val_a;
-  UV* vdst = (flips & 1) ? val_a : val_b;
-
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  unsigned* warp_hist = reinterpret_cast<unsigned*>(smem_raw);                    // [NWARPS][256]
-  unsigned* s_goff = warp_hist + NWARPS * RADIX_BINS;                              // [256] global offset - staged position
-  unsigned* s_scan = s_goff + RADIX_BINS;                                          // [8] warp totals for the digit scan
-  UK* stage_k = reinterpret_cast<UK*>(s_scan + 16);
-  UV* stage_v = reinterpret_cast<UV*>(stage_k + TILE);
-  __shared__ unsigned s_tile;
-
-  if (threadIdx.x == 0) s_tile = atomicAdd(&ctrl->tickets[pass], 1u);
-  for (int i = threadIdx.x; i < NWARPS * RADIX_BINS; i += ONESWEEP_BLOCK) warp_hist[i] = 0;
-  __syncthreads();
-  const unsigned tile = s_tile;
   const int lane = lane_id(), warp = threadIdx.x >> 5;
   const unsigned tile_base = tile * (unsigned)TILE;
-  const unsigned tile_n = min((unsigned)TILE, n - tile_base);
-  const unsigned wbase = tile_base + warp * WCHUNK;
-  const int shift = pass * RADIX_BITS;
+  const unsigned tile_n = FULL ? (unsigned)TILE : n - tile_base;
+  const unsigned wofs = warp * WCHUNK + lane;   // this lane's first item inside the tile
 
-  // ---- load keys (and values: issued now so their latency hides behind the ranking)
-  UK key[IPT]; UV val[IPT];
+  // ---- load keys, lane-interleaved inside the warp's chunk (a warp instruction is contiguous)
+  UK key[IPT];
+  const UK* ksrc = src + tile_base + wofs;
 #pragma unroll
-  for (int i = 0; i < IPT; ++i) {
-    unsigned g = wbase + i * 32 + lane;
-    key[i] = g < n ? __ldcs(src + g) : (UK)0;
-  }
-  if constexpr (HAS_V) {
-#pragma unroll
-    for (int i = 0; i < IPT; ++i) {
-      unsigned g = wbase + i * 32 + lane;
-      val[i] = g < n ? __ldcs(vsrc + g) : (UV)0;
-    }
-  }
+  for (int i = 0; i < IPT; ++i) key[i] = (FULL || wofs + i * 32 < tile_n) ? __ldcs(ksrc + i * 32) : (UK)0;
 
-  // ---- rank inside the warp: keys of equal digit find each other with match.any; the lowest
-  // lane of each group bumps the warp's private counter for that digit
-  unsigned short pos[IPT];
+  // ---- rank inside the warp: keys of equal digit find each other with ballots; the first
+  // lane of each group reserves the group's slots in the warp's private digit counters
+  unsigned pd[IPT];   // low 16 bits: position, bits 16..23: digit
   unsigned* my_hist = warp_hist + warp * RADIX_BINS;
   const unsigned lanemask_lt = (1u << lane) - 1;
 #pragma unroll
   for (int i = 0; i < IPT; ++i) {
-    unsigned g = wbase + i * 32 + lane;
-    unsigned d = g < n ? ((unsigned)(encode_key(key[i], coding) >> shift) & (RADIX_BINS - 1)) : (RADIX_BINS - 1);
-    unsigned peers = __match_any_sync(FULL_MASK, d);
-    int leader = __ffs(peers) - 1;
+    // a partial tile pads with pseudo-keys of digit 255: ranked after every real key of the tile
+    unsigned d = (FULL || wofs + i * 32 < tile_n) ? key_digit<IS_FLOAT>(key[i], shift, dmask) : (RADIX_BINS - 1);
+    // lanes holding the same digit: one ballot per digit bit.  (match.any computes this in one
+    // instruction but is issued at a small fraction of the ballot rate on sm_100.)
+    unsigned peers = FULL_MASK;
+#pragma unroll
+    for (int b = 0; b < RADIX_BITS; ++b) {
+      const bool bit = (d >> b) & 1;
+      const unsigned vote = __ballot_sync(FULL_MASK, bit);
+      peers &= bit ? vote : ~vote;
+    }
+    unsigned ahead = __popc(peers & lanemask_lt);
     unsigned before = 0;
-    if (lane == leader) { before = my_hist[d]; my_hist[d] = before + __popc(peers); }
-    before = __shfl_sync(FULL_MASK, before, leader);
-    pos[i] = (unsigned short)(before + __popc(peers & lanemask_lt));
-    __syncwarp();
+    if (ahead == 0) before = atomicAdd(&my_hist[d], (unsigned)__popc(peers));
+    before = __shfl_sync(FULL_MASK, before, __ffs(peers) - 1);
+    pd[i] = (before + ahead) | (d << 16);
   }
   __syncthreads();
 
-  // ---- per digit: stack the warps' counts, scan digits, chain to preceding tiles
+  // ---- per digit: stack the warps' counts, scan the digits, chain to the preceding tiles
   unsigned my_count = 0, digit_off = 0;
   if (threadIdx.x < RADIX_BINS) {
     unsigned run = 0;
@@ -205,67 +213,106 @@ onesweep_kernel(UK* buf_a, UK* buf_b, UV* val_a, UV* val_b, unsigned n, key_codi
   __syncthreads();
   if (threadIdx.x < RADIX_BINS) {
     for (int w = 0; w < warp; ++w) digit_off += s_scan[w];
-    // a partial tile pads with pseudo-keys of digit 255, ranked after every real key
     unsigned real_count = my_count;
-    if (threadIdx.x == RADIX_BINS - 1) real_count -= (unsigned)TILE - tile_n;
+    if (!FULL && threadIdx.x == RADIX_BINS - 1) real_count -= (unsigned)TILE - tile_n;
     LB* slot = lookback + (size_t)tile * RADIX_BINS + threadIdx.x;
     LB prefix = 0;
     if (tile == 0) {
       *reinterpret_cast<volatile LB*>(slot) = ((LB)TILE_INCLUSIVE << LB_BITS) | (LB)real_count;
     } else {
       *reinterpret_cast<volatile LB*>(slot) = ((LB)TILE_AGGREGATE << LB_BITS) | (LB)real_count;
-      long long t = (long long)tile - 1;
+      const volatile LB* look = slot - RADIX_BINS;
       unsigned iter = 0;
       while (true) {
-        LB w = *reinterpret_cast<volatile LB*>(lookback + (size_t)t * RADIX_BINS + threadIdx.x);
+        LB w = *look;
         unsigned st = (unsigned)(w >> LB_BITS);
         if (st == TILE_INVALID) {
-          if (++iter > SPIN_LIMIT) { record_error(&hdr->error, ERR_LOOKBACK_TIMEOUT); break; }
+          if (++iter > SPIN_LIMIT) { record_error(err, ERR_LOOKBACK_TIMEOUT); break; }
           backoff(iter);
           continue;
         }
         prefix += w & LB_MASK;
         if (st == TILE_INCLUSIVE) break;
-        --t; iter = 0;
+        look -= RADIX_BINS; iter = 0;
       }
       *reinterpret_cast<volatile LB*>(slot) = ((LB)TILE_INCLUSIVE << LB_BITS) | (LB)(prefix + real_count);
     }
-    s_goff[threadIdx.x] = (unsigned)ctrl->hist[pass][threadIdx.x] + (unsigned)prefix - digit_off;
+    s_goff[threadIdx.x] = (unsigned)bin_base[threadIdx.x] + (unsigned)prefix - digit_off;
 #pragma unroll
     for (int w = 0; w < NWARPS; ++w) warp_hist[w * RADIX_BINS + threadIdx.x] += digit_off;
   }
   __syncthreads();
 
-  // ---- stage keys in bucket order, then stream each bucket's run out contiguously
+  // ---- stage keys in bucket order; fetch the values while the keys stream out
 #pragma unroll
   for (int i = 0; i < IPT; ++i) {
-    unsigned g = wbase + i * 32 + lane;
-    unsigned d = g < n ? ((unsigned)(encode_key(key[i], coding) >> shift) & (RADIX_BINS - 1)) : (RADIX_BINS - 1);
-    pos[i] = (unsigned short)(pos[i] + my_hist[d]);
-    stage_k[pos[i]] = key[i];
+    unsigned p = (pd[i] & 0xffffu) + my_hist[pd[i] >> 16];
+    pd[i] = p;
+    stage_k[p] = key[i];
+  }
+  UV val[HAS_V ? IPT : 1];
+  if constexpr (HAS_V) {
+    const UV* vs = vsrc + tile_base + wofs;
+#pragma unroll
+    for (int i = 0; i < IPT; ++i) val[i] = (FULL || wofs + i * 32 < tile_n) ? __ldcs(vs + i * 32) : (UV)0;
   }
   __syncthreads();
-  unsigned char dig[IPT];
+  // consecutive threads take consecutive staged slots, so each bucket's run is written contiguously
 #pragma unroll
   for (int i = 0; i < IPT; ++i) {
     unsigned j = threadIdx.x + i * ONESWEEP_BLOCK;
-    if (j < tile_n) {
+    if (FULL || j < tile_n) {
       UK k = stage_k[j];
-      unsigned d = (unsigned)(encode_key(k, coding) >> shift) & (RADIX_BINS - 1);
-      dig[i] = (unsigned char)d;
-      dst[s_goff[d] + j] = k;
+      dst[s_goff[key_digit<IS_FLOAT>(k, shift, dmask)] + j] = k;
     }
   }
   if constexpr (HAS_V) {
 #pragma unroll
-    for (int i = 0; i < IPT; ++i) stage_v[pos[i]] = val[i];
+    for (int i = 0; i < IPT; ++i) stage_v[pd[i]] = val[i];
     __syncthreads();
 #pragma unroll
     for (int i = 0; i < IPT; ++i) {
       unsigned j = threadIdx.x + i * ONESWEEP_BLOCK;
-      if (j < tile_n) vdst[s_goff[dig[i]] + j] = stage_v[j];
+      if (FULL || j < tile_n) vdst[s_goff[key_digit<IS_FLOAT>(stage_k[j], shift, dmask)] + j] = stage_v[j];
     }
   }
+}
+
+template <class UK, class UV, bool HAS_V, bool IS_FLOAT, class LB, int IPT>
+__global__ void __launch_bounds__(ONESWEEP_BLOCK, 2)
+onesweep_kernel(UK* buf_a, UK* buf_b, UV* val_a, UV* val_b, unsigned n, key_coding coding, int pass, int first_pass,
+                radix_ctrl* ctrl, LB* lookback, ws_header* hdr) {
+  constexpr int NWARPS = ONESWEEP_BLOCK / 32;
+  constexpr int TILE = ONESWEEP_BLOCK * IPT;
+  if (ctrl->skip[pass]) return;
+  int flips = 0;
+  for (int q = first_pass; q < pass; ++q) flips += ctrl->skip[q] ? 0 : 1;
+  const UK* src = (flips & 1) ? buf_b : buf_a;
+  UK* dst = (flips & 1) ? buf_a : buf_b;
+  const UV* vsrc = (flips & 1) ? val_b : val_a;
+  UV* vdst = (flips & 1) ? val_a : val_b;
+
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  unsigned* warp_hist = reinterpret_cast<unsigned*>(smem_raw);   // [NWARPS][256]
+  unsigned* s_goff = warp_hist + NWARPS * RADIX_BINS;   // [256] bucket's global offset minus its staged offset
+  unsigned* s_scan = s_goff + RADIX_BINS;                         // [16]
+  UK* stage_k = reinterpret_cast<UK*>(s_scan + 16);
+  UV* stage_v = reinterpret_cast<UV*>(stage_k + TILE);
+  __shared__ unsigned s_tile;
+
+  if (threadIdx.x == 0) s_tile = atomicAdd(&ctrl->tickets[pass], 1u);
+  for (int i = threadIdx.x; i < NWARPS * RADIX_BINS; i += ONESWEEP_BLOCK) warp_hist[i] = 0;
+  __syncthreads();
+  const unsigned tile = s_tile;
+  const int shift = pass * RADIX_BITS;
+  const unsigned dmask = digit_mask<UK>(coding, shift);
+  const bool full = (unsigned long long)(tile + 1) * TILE <= n;
+  if (full)
+    onesweep_tile<UK, UV, HAS_V, IS_FLOAT, LB, IPT, true>(src, dst, vsrc, vdst, n, tile, shift, dmask, ctrl->hist[pass], lookback, &hdr->error,
+                                                          warp_hist, s_goff, s_scan, stage_k, stage_v);
+  else
+    onesweep_tile<UK, UV, HAS_V, IS_FLOAT, LB, IPT, false>(src, dst, vsrc, vdst, n, tile, shift, dmask, ctrl->hist[pass], lookback, &hdr->error,
+                                                           warp_hist, s_goff, s_scan, stage_k, stage_v);
 }
 
 // ---------------------------------------------------------------- 4. copy back after an odd number of passes
@@ -320,21 +367,20 @@ cudaError_t radix_sort_async(UK* keys_a, UK* keys_b, UV* vals_a, UV* vals_b, siz
   if (e != cudaSuccess) return e;
 
   const device_info& di = current_device_info();
-  size_t hist_grid = (n + HIST_BLOCK * 4 - 1) / (HIST_BLOCK * 4);
-  if (hist_grid > (size_t)di.sm_count * 4) hist_grid = (size_t)di.sm_count * 4;
-  radix_hist_kernel<UK><<<(unsigned)hist_grid, HIST_BLOCK, 0, stream>>>(keys_a, n, coding, first_pass, num_passes, ctrl);
+  size_t hist_grid = (n + HIST_BLOCK * 16 - 1) / (HIST_BLOCK * 16);
+  if (hist_grid > (size_t)di.sm_count) hist_grid = (size_t)di.sm_count;
+  const size_t hist_smem = (size_t)KB * RADIX_BINS * hist_tuning<UK>::COPIES * 4;
+  auto hk = coding.kind == KEY_FLOAT ? radix_hist_kernel<UK, true> : radix_hist_kernel<UK, false>;
+  if ((e = cudaFuncSetAttribute(hk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hist_smem)) != cudaSuccess) return e;
+  hk<<<(unsigned)hist_grid, HIST_BLOCK, hist_smem, stream>>>(keys_a, n, coding, first_pass, num_passes, ctrl);
   radix_scan_hist_kernel<<<num_passes, RADIX_BINS, 0, stream>>>(ctrl, n, first_pass);
 
   const size_t smem = onesweep_smem_bytes<KB, VB>();
-  auto k32 = onesweep_kernel<UK, UV, HAS_V, uint32_t, IPT>;
-  auto k64 = onesweep_kernel<UK, UV, HAS_V, unsigned long long, IPT>;
-  static thread_local bool attr_done[64] = {false};
-  int dev = 0; cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-    if ((e = cudaFuncSetAttribute(k32, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
-    if ((e = cudaFuncSetAttribute(k64, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
-    attr_done[dev] = true;
-  }
+  const bool isf = coding.kind == KEY_FLOAT;
+  auto k32 = isf ? onesweep_kernel<UK, UV, HAS_V, true, uint32_t, IPT> : onesweep_kernel<UK, UV, HAS_V, false, uint32_t, IPT>;
+  auto k64 = isf ? onesweep_kernel<UK, UV, HAS_V, true, unsigned long long, IPT> : onesweep_kernel<UK, UV, HAS_V, false, unsigned long long, IPT>;
+  // opting in to large dynamic shared memory is per kernel and per device; it is cheap, so do it every call
+  if ((e = cudaFuncSetAttribute(lb32 ? (const void*)k32 : (const void*)k64, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
   for (int p = 0; p < num_passes; ++p) {
     char* lb = lb0 + lb_bytes * p;
     if (lb32)
