@@ -76,6 +76,44 @@ int tb200_sort_by_key(void* d_keys, void* d_keys_alt, void* d_vals, void* d_vals
                       int key_t, int val_bytes, int descending, int begin_bit, int end_bit,
                       void* d_ws, size_t* ws_bytes, tb200_stream_t stream);
 
+/* thrust::copy_if(first, last, [stencil,] result, pred) -- thrust/system/cuda/detail/copy_if.h:
+ * 780-853.  Stable.  Without a stencil (d_stencil == NULL) the predicate tests the element; with
+ * one it tests stencil[i] (stencil_t: U8 or I32) and copies in[i].  The number of elements
+ * written goes to *d_count (device, may be NULL) and to the workspace header.  d_out == d_in is
+ * allowed (the remove_if use of thrust/system/cuda/detail/remove.h:38-65). */
+int tb200_copy_if(const void* d_in, const void* d_stencil, void* d_out, size_t n, int t,
+                  int stencil_t, int pred, long long a, long long b, unsigned long long* d_count,
+                  void* d_ws, size_t* ws_bytes, tb200_stream_t stream);
+
+/* thrust::stable_partition_copy / partition_copy(first, last, [stencil,] out_true, out_false,
+ * pred) -- thrust/system/cuda/detail/partition.h:909-1075.  Both outputs keep input order.
+ * *d_count = number of elements written to d_out_true. */
+int tb200_partition_copy(const void* d_in, const void* d_stencil, void* d_out_true,
+                         void* d_out_false, size_t n, int t, int stencil_t, int pred, long long a,
+                         long long b, unsigned long long* d_count, void* d_ws, size_t* ws_bytes,
+                         tb200_stream_t stream);
+
+/* thrust::partition / thrust::stable_partition(first, last, pred), in place --
+ * thrust/system/cuda/detail/partition.h:833-907 and :1077-1132.  Always stable (which satisfies
+ * both).  The workspace includes room for a copy of the data, like the reference's temporary
+ * (partition.h:808-810).  *d_count = number of elements satisfying pred (the split point). */
+int tb200_partition(void* d_data, size_t n, int t, int pred, long long a, long long b,
+                    unsigned long long* d_count, void* d_ws, size_t* ws_bytes,
+                    tb200_stream_t stream);
+
+/* thrust::unique_copy(first, last, result) with equal_to; d_out == d_in is thrust::unique --
+ * thrust/system/cuda/detail/unique.h:710-795.  *d_count = number of elements kept. */
+int tb200_unique_copy(const void* d_in, void* d_out, size_t n, int t, unsigned long long* d_count,
+                      void* d_ws, size_t* ws_bytes, tb200_stream_t stream);
+
+/* thrust::reduce_by_key(keys, keys + n, vals, keys_out, vals_out, equal_to, op) --
+ * thrust/system/cuda/detail/reduce_by_key.h:1063-1161.  key_t: any dtype; val_t: I32 U32 I64 U64
+ * F32 F64; values of a run are combined left to right.  *d_count = number of runs.  n < 2^31,
+ * as in the reference (reduce_by_key.h:983). */
+int tb200_reduce_by_key(const void* d_keys, const void* d_vals, void* d_keys_out, void* d_vals_out,
+                        size_t n, int key_t, int val_t, int op, unsigned long long* d_count,
+                        void* d_ws, size_t* ws_bytes, tb200_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

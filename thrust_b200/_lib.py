@@ -9,7 +9,7 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libthrust_b200.so")
 
-_vp, _sz, _i = C.c_void_p, C.c_size_t, C.c_int
+_vp, _sz, _i, _ll = C.c_void_p, C.c_size_t, C.c_int, C.c_longlong
 _szp = C.POINTER(C.c_size_t)
 
 # name -> argtypes; every function returns int (cudaError_t)
@@ -21,6 +21,11 @@ PROTOTYPES = {
     "tb200_inclusive_scan": [_vp, _vp, _sz, _i, _i, _vp, _szp, _vp],
     "tb200_exclusive_scan": [_vp, _vp, _sz, _i, _i, _vp, _vp, _szp, _vp],
     "tb200_sort_by_key": [_vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _vp, _szp, _vp],
+    "tb200_copy_if": [_vp, _vp, _vp, _sz, _i, _i, _i, _ll, _ll, _vp, _vp, _szp, _vp],
+    "tb200_partition_copy": [_vp, _vp, _vp, _vp, _sz, _i, _i, _i, _ll, _ll, _vp, _vp, _szp, _vp],
+    "tb200_partition": [_vp, _sz, _i, _i, _ll, _ll, _vp, _vp, _szp, _vp],
+    "tb200_unique_copy": [_vp, _vp, _sz, _i, _vp, _vp, _szp, _vp],
+    "tb200_reduce_by_key": [_vp, _vp, _vp, _vp, _sz, _i, _i, _i, _vp, _vp, _szp, _vp],
 }
 
 _lib = None

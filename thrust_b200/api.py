@@ -160,3 +160,78 @@ def sort_by_key(keys, vals, descending=False, begin_bit=0, end_bit=None):
 
 
 stable_sort_by_key = sort_by_key
+
+
+# ------------------------------------------------------------------------------------- compaction
+def _count_word():
+    return torch.zeros(1, dtype=torch.int64, device="cuda")
+
+
+def _read_count(cnt):
+    return int(cnt.cpu().item())
+
+
+def copy_if(x, pred, a=0, b=0, stencil=None, out=None):
+    """thrust::copy_if(first, last, [stencil,] result, pred): returns out[:count] (stable)."""
+    _require_cuda(x, stencil, out)
+    out = torch.empty_like(x) if out is None else out
+    cnt = _count_word()
+    ws = _call_with_ws("select", "tb200_copy_if", _ptr(x), _ptr(stencil), _ptr(out), x.numel(), DTYPE_CODE[x.dtype],
+                       0 if stencil is None else DTYPE_CODE[stencil.dtype], PREDS[pred], a, b, _ptr(cnt))
+    _sync_and_check(ws, "copy_if")
+    return out[:_read_count(cnt)]
+
+
+def partition_copy(x, pred, a=0, b=0, stencil=None):
+    """thrust::stable_partition_copy: returns (selected, rejected), both in input order."""
+    _require_cuda(x, stencil)
+    out_t, out_f = torch.empty_like(x), torch.empty_like(x)
+    cnt = _count_word()
+    ws = _call_with_ws("select", "tb200_partition_copy", _ptr(x), _ptr(stencil), _ptr(out_t), _ptr(out_f), x.numel(),
+                       DTYPE_CODE[x.dtype], 0 if stencil is None else DTYPE_CODE[stencil.dtype], PREDS[pred], a, b, _ptr(cnt))
+    _sync_and_check(ws, "partition_copy")
+    k = _read_count(cnt)
+    return out_t[:k], out_f[:x.numel() - k]
+
+
+stable_partition_copy = partition_copy
+
+
+def partition(x, pred, a=0, b=0):
+    """thrust::partition / thrust::stable_partition in place; returns the split point."""
+    _require_cuda(x)
+    cnt = _count_word()
+    ws = _call_with_ws("partition", "tb200_partition", _ptr(x), x.numel(), DTYPE_CODE[x.dtype], PREDS[pred], a, b, _ptr(cnt))
+    _sync_and_check(ws, "partition")
+    return _read_count(cnt)
+
+
+stable_partition = partition
+
+
+def unique_copy(x, out=None):
+    """thrust::unique_copy(first, last, result): returns out[:count]."""
+    _require_cuda(x, out)
+    out = torch.empty_like(x) if out is None else out
+    cnt = _count_word()
+    ws = _call_with_ws("select", "tb200_unique_copy", _ptr(x), _ptr(out), x.numel(), DTYPE_CODE[x.dtype], _ptr(cnt))
+    _sync_and_check(ws, "unique_copy")
+    return out[:_read_count(cnt)]
+
+
+def unique(x):
+    """thrust::unique(first, last) in place: returns x[:count]."""
+    return unique_copy(x, out=x)
+
+
+def reduce_by_key(keys, vals, op="plus"):
+    """thrust::reduce_by_key(keys_first, keys_last, values_first, keys_out, values_out, equal_to, op):
+    returns (keys_out[:runs], values_out[:runs])."""
+    _require_cuda(keys, vals)
+    ko, vo = torch.empty_like(keys), torch.empty_like(vals)
+    cnt = _count_word()
+    ws = _call_with_ws("rbk", "tb200_reduce_by_key", _ptr(keys), _ptr(vals), _ptr(ko), _ptr(vo), keys.numel(),
+                       DTYPE_CODE[keys.dtype], DTYPE_CODE[vals.dtype], OPS[op], _ptr(cnt))
+    _sync_and_check(ws, "reduce_by_key")
+    k = _read_count(cnt)
+    return ko[:k], vo[:k]
