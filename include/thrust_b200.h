@@ -114,6 +114,26 @@ int tb200_reduce_by_key(const void* d_keys, const void* d_vals, void* d_keys_out
                         size_t n, int key_t, int val_t, int op, unsigned long long* d_count,
                         void* d_ws, size_t* ws_bytes, tb200_stream_t stream);
 
+/* thrust::merge / thrust::merge_by_key(A, B, [payload A, payload B,] out, [payload out,] comp)
+ * with thrust::less (descending=0) or thrust::greater (descending=1) --
+ * thrust/system/cuda/detail/merge.h:862-1013.  Both inputs must already be sorted by comp.
+ * Stable: on equal keys the element of A comes first (merge.h:70-84).  key_t: I32 U32 I64 U64 F32
+ * F64; val_bytes: 0 (keys only), 4 or 8.  Outputs must not overlap the inputs. */
+int tb200_merge_by_key(const void* d_keys_a, const void* d_vals_a, size_t na, const void* d_keys_b,
+                       const void* d_vals_b, size_t nb, void* d_keys_out, void* d_vals_out,
+                       int key_t, int val_bytes, int descending, void* d_ws, size_t* ws_bytes,
+                       tb200_stream_t stream);
+
+/* The comparison-sort route of thrust::stable_sort / stable_sort_by_key --
+ * thrust/system/cuda/detail/sort.h:1278-1321 (__merge_sort::merge_sort), the path the reference
+ * takes for user comparators and non-arithmetic keys.  Here the comparator is less / greater on
+ * the key; payloads move with their keys, which is exactly
+ * stable_sort(zip(keys, vals), [](a, b){ return get<0>(a) < get<0>(b); }).  In place; d_keys_alt /
+ * d_vals_alt are same-sized scratch (sort.h:1200-1205).  Types as tb200_merge_by_key. */
+int tb200_merge_sort_by_key(void* d_keys, void* d_keys_alt, void* d_vals, void* d_vals_alt, size_t n,
+                            int key_t, int val_bytes, int descending, void* d_ws, size_t* ws_bytes,
+                            tb200_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

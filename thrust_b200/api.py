@@ -235,3 +235,47 @@ def reduce_by_key(keys, vals, op="plus"):
     _sync_and_check(ws, "reduce_by_key")
     k = _read_count(cnt)
     return ko[:k], vo[:k]
+
+
+# ------------------------------------------------------------------------------------- merge
+def merge_by_key(keys_a, keys_b, vals_a=None, vals_b=None, descending=False):
+    """thrust::merge_by_key(A, B, payload A, payload B, keys_out, payload_out[, greater]); with no
+    payloads it is thrust::merge.  Returns (keys_out, payload_out or None)."""
+    _require_cuda(keys_a, keys_b, vals_a, vals_b)
+    if keys_a.dtype != keys_b.dtype:
+        raise ValueError("key types differ")
+    na, nb = keys_a.numel(), keys_b.numel()
+    ko = torch.empty(na + nb, dtype=keys_a.dtype, device=keys_a.device)
+    vo = None if vals_a is None else torch.empty(na + nb, dtype=vals_a.dtype, device=keys_a.device)
+    vb = 0 if vals_a is None else vals_a.element_size()
+    ws = _call_with_ws("merge", "tb200_merge_by_key", _ptr(keys_a), _ptr(vals_a), na, _ptr(keys_b), _ptr(vals_b), nb, _ptr(ko),
+                       _ptr(vo), DTYPE_CODE[keys_a.dtype], vb, int(descending))
+    _sync_and_check(ws, "merge_by_key")
+    return ko, vo
+
+
+def merge(a, b, descending=False):
+    """thrust::merge(A, B, out[, greater])."""
+    return merge_by_key(a, b, None, None, descending)[0]
+
+
+def merge_sort_by_key(keys, vals=None, descending=False):
+    """The comparison-sort route of thrust::stable_sort(_by_key): stable merge sort in place."""
+    _require_cuda(keys, vals)
+    n = keys.numel()
+    vb = 0 if vals is None else vals.element_size()
+    kalt = workspaces.get("sort_keys_alt", n * keys.element_size())
+    valt = None if vals is None else workspaces.get("sort_vals_alt", n * vb)
+    ws = _call_with_ws("merge_sort", "tb200_merge_sort_by_key", _ptr(keys), _ptr(kalt), _ptr(vals), _ptr(valt), n,
+                       DTYPE_CODE[keys.dtype], vb, int(descending))
+    _sync_and_check(ws, "merge_sort_by_key")
+    return keys, vals
+
+
+def stable_sort_zip_by_first(keys, vals, method="merge"):
+    """thrust::stable_sort(zip(keys, vals), comp) with comp ordering on get<0> alone, in place.
+    method "merge" follows the reference's comparator route (merge sort); "radix" uses the fact
+    that the comparator is a plain less on an arithmetic key and takes the radix path."""
+    if method == "radix":
+        return sort_by_key(keys, vals)
+    return merge_sort_by_key(keys, vals)
