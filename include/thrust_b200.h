@@ -59,9 +59,11 @@ int tb200_reduce(const void* d_in, size_t n, int in_t, int acc_t, int op, const 
 
 /* thrust::inclusive_scan / thrust::exclusive_scan -- thrust/system/cuda/detail/scan.h:215-361
  * (cuda_cub::inclusive_scan_n, exclusive_scan_n).  Element type t (I32 U32 I64 U64 F32 F64) for
- * input, output and accumulator.  d_in == d_out is allowed. */
-int tb200_inclusive_scan(const void* d_in, void* d_out, size_t n, int t, int op, void* d_ws,
-                         size_t* ws_bytes, tb200_stream_t stream);
+ * input, output and accumulator.  d_in == d_out is allowed.  h_init of the inclusive scan may be
+ * NULL (the classic form); when given, it is combined in front of the first element, which is how
+ * a shard of a multi-GPU scan receives the carry of the shards before it. */
+int tb200_inclusive_scan(const void* d_in, void* d_out, size_t n, int t, int op, const void* h_init,
+                         void* d_ws, size_t* ws_bytes, tb200_stream_t stream);
 int tb200_exclusive_scan(const void* d_in, void* d_out, size_t n, int t, int op,
                          const void* h_init, void* d_ws, size_t* ws_bytes, tb200_stream_t stream);
 
@@ -133,6 +135,24 @@ int tb200_merge_by_key(const void* d_keys_a, const void* d_vals_a, size_t na, co
 int tb200_merge_sort_by_key(void* d_keys, void* d_keys_alt, void* d_vals, void* d_vals_alt, size_t n,
                             int key_t, int val_bytes, int descending, void* d_ws, size_t* ws_bytes,
                             tb200_stream_t stream);
+
+/* Batched lower bound: d_out[j] = number of elements of the sorted range d_sorted[0, n) that
+ * order strictly before d_needles[j] (thrust::lower_bound with less / greater).  Used by the
+ * multi-GPU sort to cut each GPU's sorted shard at the splitters.  key_t: I32 U32 I64 U64 F32 F64.
+ * Has no counterpart among the reference files on the hot path (the reference's vectorised
+ * binary search is thrust/system/cuda/detail/binary_search.h). */
+int tb200_lower_bound(const void* d_sorted, size_t n, const void* d_needles, size_t m,
+                      unsigned long long* d_out, int key_t, int descending, tb200_stream_t stream);
+
+/* Per-kernel device timing, off by default.  tb200_kernel_timing(1) makes every launcher bracket
+ * its dominant kernel with CUDA events on the launching stream (and clears earlier records);
+ * tb200_kernel_timing_read waits for the recorded launches and returns up to `capacity` pairs
+ * (kernel id, milliseconds), then clears the records.  Kernel ids: 1 reduce, 2 scan, 3 onesweep
+ * pass, 4 radix histogram, 5 compaction, 6 reduce_by_key, 7 merge, 8 block sort.  This is the
+ * library's counterpart of the reference's THRUST_DEBUG_SYNC launch log
+ * (thrust/system/cuda/detail/core/agent_launcher.h:518-590).  At most 256 launches are kept. */
+int tb200_kernel_timing(int enable);
+int tb200_kernel_timing_read(int capacity, int* h_kernel_ids, float* h_ms, int* h_count);
 
 #ifdef __cplusplus
 }

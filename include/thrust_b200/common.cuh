@@ -51,6 +51,39 @@ inline const device_info& current_device_info() {
   return cache[dev];
 }
 
+// ---------------------------------------------------------------- optional per-kernel timing
+// When switched on, launchers bracket their dominant kernel with CUDA events on the launching
+// stream so that a caller can read each launch's device time afterwards (the library's analogue of
+// the reference's THRUST_DEBUG_SYNC launch log, thrust/system/cuda/detail/core/agent_launcher.h:
+// 518-590).  Off by default: no events are created or recorded.
+enum kernel_id : int {
+  KID_REDUCE = 1, KID_SCAN = 2, KID_ONESWEEP = 3, KID_RADIX_HIST = 4, KID_SELECT = 5, KID_REDUCE_BY_KEY = 6,
+  KID_MERGE = 7, KID_BLOCK_SORT = 8
+};
+struct kernel_timer {
+  static constexpr int CAP = 256;
+  bool enabled = false;
+  int used = 0;
+  int ids[CAP];
+  cudaEvent_t start[CAP], stop[CAP];
+  bool created[CAP] = {false};
+  int begin(int id, cudaStream_t s) {
+    if (!enabled || used >= CAP) return -1;
+    int i = used++;
+    if (!created[i]) { cudaEventCreate(&start[i]); cudaEventCreate(&stop[i]); created[i] = true; }
+    ids[i] = id;
+    cudaEventRecord(start[i], s);
+    return i;
+  }
+  void end(int i, cudaStream_t s) { if (i >= 0) cudaEventRecord(stop[i], s); }
+};
+inline kernel_timer& global_kernel_timer() { static kernel_timer t; return t; }
+struct timed_launch {
+  int slot; cudaStream_t s;
+  timed_launch(int id, cudaStream_t stream) : slot(global_kernel_timer().begin(id, stream)), s(stream) {}
+  ~timed_launch() { global_kernel_timer().end(slot, s); }
+};
+
 // ---------------------------------------------------------------- functors
 struct plus_op { template <class T> __host__ __device__ T operator()(const T& a, const T& b) const { return a + b; } };
 struct min_op { template <class T> __host__ __device__ T operator()(const T& a, const T& b) const { return b < a ? b : a; } };

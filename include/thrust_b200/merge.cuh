@@ -177,6 +177,7 @@ cudaError_t merge_pass_async(KeyItA ka, KeyItB kb, ValItA va, ValItB vb, KeyOutI
   const size_t tiles = g.num_tiles();
   size_t* a_split = reinterpret_cast<size_t*>(static_cast<char*>(ws) + sizeof(ws_header));
   merge_partition_kernel<KeyItA, KeyItB, Comp, TILE><<<(unsigned)((tiles + 255) / 256), 256, 0, stream>>>(ka, kb, g, tiles, comp, a_split);
+  timed_launch tl(KID_MERGE, stream);
   merge_kernel<KeyItA, KeyItB, ValItA, ValItB, KeyOutIt, ValOutIt, K, V, HAS_V, Comp, IPT>
       <<<(unsigned)tiles, MERGE_BLOCK, 0, stream>>>(ka, kb, va, vb, ko, vo, g, comp, a_split);
   return cudaGetLastError();
@@ -301,7 +302,8 @@ cudaError_t merge_sort_async(K* keys, K* keys_alt, V* vals, V* vals_alt, size_t 
   V* cur_v = (passes & 1) ? vals_alt : vals;
   K* oth_k = (passes & 1) ? keys : keys_alt;
   V* oth_v = (passes & 1) ? vals : vals_alt;
-  block_sort_kernel<const K*, const V*, K*, V*, K, V, HAS_V, Comp, BS_IPT><<<(unsigned)tiles, MERGE_BLOCK, 0, stream>>>(keys, vals, cur_k, cur_v, n, comp);
+  { timed_launch tl(KID_BLOCK_SORT, stream);
+  block_sort_kernel<const K*, const V*, K*, V*, K, V, HAS_V, Comp, BS_IPT><<<(unsigned)tiles, MERGE_BLOCK, 0, stream>>>(keys, vals, cur_k, cur_v, n, comp); }
   if ((e = cudaGetLastError()) != cudaSuccess) return e;
   for (size_t run = BS_TILE; run < n; run <<= 1) {
     constexpr int TILE = merge_tile_items<K, V, HAS_V>();

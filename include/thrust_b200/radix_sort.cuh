@@ -372,7 +372,8 @@ cudaError_t radix_sort_async(UK* keys_a, UK* keys_b, UV* vals_a, UV* vals_b, siz
   const size_t hist_smem = (size_t)KB * RADIX_BINS * hist_tuning<UK>::COPIES * 4;
   auto hk = coding.kind == KEY_FLOAT ? radix_hist_kernel<UK, true> : radix_hist_kernel<UK, false>;
   if ((e = cudaFuncSetAttribute(hk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hist_smem)) != cudaSuccess) return e;
-  hk<<<(unsigned)hist_grid, HIST_BLOCK, hist_smem, stream>>>(keys_a, n, coding, first_pass, num_passes, ctrl);
+  { timed_launch tl(KID_RADIX_HIST, stream);
+  hk<<<(unsigned)hist_grid, HIST_BLOCK, hist_smem, stream>>>(keys_a, n, coding, first_pass, num_passes, ctrl); }
   radix_scan_hist_kernel<<<num_passes, RADIX_BINS, 0, stream>>>(ctrl, n, first_pass);
 
   const size_t smem = onesweep_smem_bytes<KB, VB>();
@@ -383,6 +384,7 @@ cudaError_t radix_sort_async(UK* keys_a, UK* keys_b, UV* vals_a, UV* vals_b, siz
   if ((e = cudaFuncSetAttribute(lb32 ? (const void*)k32 : (const void*)k64, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
   for (int p = 0; p < num_passes; ++p) {
     char* lb = lb0 + lb_bytes * p;
+    timed_launch tl(KID_ONESWEEP, stream);
     if (lb32)
       k32<<<(unsigned)tiles, ONESWEEP_BLOCK, smem, stream>>>(keys_a, keys_b, vals_a, vals_b, (unsigned)n, coding, first_pass + p, first_pass, ctrl,
                                                             reinterpret_cast<uint32_t*>(lb), hdr);

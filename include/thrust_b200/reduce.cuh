@@ -136,12 +136,14 @@ cudaError_t reduce_async(InIt in, size_t n, AccT init, Op op, AccT* d_out, void*
       if (is_aligned16(in)) {
         constexpr int VEC = 16 / sizeof(In);
         int grid = reduce_grid(n / VEC);
+        timed_launch tl(KID_REDUCE, stream);
         reduce_kernel<InIt, AccT, Op, VEC><<<grid, REDUCE_BLOCK, 0, stream>>>(in, n, init, op, partials, has, &hdr->ticket, d_out);
         return cudaGetLastError();
       }
     }
   }
   int grid = reduce_grid(n);
+  timed_launch tl(KID_REDUCE, stream);
   reduce_kernel<InIt, AccT, Op, 0><<<grid, REDUCE_BLOCK, 0, stream>>>(in, n, init, op, partials, has, &hdr->ticket, d_out);
   return cudaGetLastError();
 }

@@ -185,6 +185,7 @@ cudaError_t reduce_by_key_async(KeyIt keys, ValIt vals, KeyOutIt keys_out, ValOu
     constexpr int VEC = decltype(vec_tag)::value;
     tile_state<rbk_pair<Off, V>> ts;
     ts.bind(base + sizeof(ws_header), tiles + 1);
+    timed_launch tl(KID_REDUCE_BY_KEY, stream);
     reduce_by_key_kernel<KeyIt, ValIt, KeyOutIt, ValOutIt, K, V, Eq, Op, Off, VEC, IPT>
         <<<(unsigned)tiles, RBK_BLOCK, 0, stream>>>(keys, vals, keys_out, vals_out, n, eq, op, ts, hdr, d_count);
   };

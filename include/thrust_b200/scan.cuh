@@ -126,6 +126,7 @@ cudaError_t scan_async(InIt in, OutIt out, size_t n, T init, bool has_init, Op o
   ts.bind(base + sizeof(ws_header), tiles + 1);
   cudaError_t e = cudaMemsetAsync(base, 0, scan_workspace_bytes<T>(n), stream);
   if (e != cudaSuccess) return e;
+  timed_launch tl(KID_SCAN, stream);
   constexpr bool ptrs = std::is_pointer<InIt>::value && std::is_pointer<OutIt>::value;
   if constexpr (ptrs) {
     using In = typename std::remove_cv<typename std::remove_pointer<InIt>::type>::type;

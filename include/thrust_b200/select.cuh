@@ -179,6 +179,7 @@ cudaError_t select_async(InIt in, StIt stencil, SelIt out_sel, RejIt out_rej, si
     constexpr int VEC = decltype(vec_tag)::value;
     tile_state<Off> ts;
     ts.bind(base + sizeof(ws_header), tiles + 1);
+    timed_launch tl(KID_SELECT, stream);
     select_kernel<MODE, KEEP_REJECTS, InIt, StIt, SelIt, RejIt, T, Pred, Off, VEC, IPT>
         <<<(unsigned)tiles, SELECT_BLOCK, 0, stream>>>(in, stencil, out_sel, out_rej, n, pred, ts, hdr, d_count, mirrored);
   };

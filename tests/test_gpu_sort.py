@@ -1,0 +1,147 @@
+"""Parity of the CUDA sorts (radix and merge sort, through the C ABI) with the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+from thrust_b200 import datagen as dg
+from gpu_util import EDGE_SIZES, dev, host, rand_of
+
+pytestmark = pytest.mark.gpu
+KEY_TYPES = [np.int32, np.uint32, np.float32, np.int64, np.uint64, np.float64]
+
+
+@pytest.mark.parametrize("n", EDGE_SIZES)
+def test_sort_by_key_u32_bit_exact_and_stable(tb, oracles, n):
+    k = dg.sort_keys_u32(n)
+    v = np.arange(n, dtype=np.uint32)             # value = original index: equality proves stability
+    kd, vd = dev(k), dev(v)
+    tb.sort_by_key(kd, vd)
+    for o in oracles:
+        ok, ov = o.sort_by_key(k, v)
+        assert np.array_equal(host(kd), ok) and np.array_equal(host(vd), ov)
+
+
+@pytest.mark.parametrize("n", [0, 1, 1000, 8193, 200003])
+def test_sort_by_key_u64_40bit_skips_empty_digits(tb, port, n):
+    k = dg.sort_keys_u64_40bit(n)
+    v = np.arange(n, dtype=np.uint32)
+    kd, vd = dev(k), dev(v)
+    tb.sort_by_key(kd, vd)
+    ok, ov = port.sort_by_key(k, v)
+    assert np.array_equal(host(kd), ok) and np.array_equal(host(vd), ov)
+
+
+def test_sort_all_key_types_orders_and_payloads(tb, port):
+    n = 70001
+    for dt in KEY_TYPES:
+        k = rand_of(dt, n, 51)
+        for desc in (False, True):
+            kd = dev(k)
+            tb.sort(kd, desc)
+            ok, _ = port.sort_by_key(k, None, desc)
+            assert np.array_equal(host(kd), ok), (dt, desc)
+            for vt in (np.uint32, np.uint64):
+                few = rand_of(dt, n, 52, small=True)   # many equal keys: stability visible
+                v = np.arange(n, dtype=vt)
+                kd, vd = dev(few), dev(v)
+                tb.sort_by_key(kd, vd, desc)
+                ok, ov = port.sort_by_key(few, v, desc)
+                assert np.array_equal(host(kd), ok) and np.array_equal(host(vd), ov), (dt, vt, desc)
+
+
+def test_sort_special_values(tb, port):
+    k = np.array([3.5, -0.0, 0.0, -1e30, np.inf, -np.inf, 1e-40, -1e-40, 2.0, -2.0], np.float32)
+    k = np.concatenate([k, rand_of(np.float32, 5000, 53)])
+    v = np.arange(k.size, dtype=np.uint32)
+    kd, vd = dev(k), dev(v)
+    tb.sort_by_key(kd, vd)
+    ok, ov = port.sort_by_key(k, v)                    # the radix code puts -0.0 before +0.0 on both sides
+    assert np.array_equal(host(kd).view(np.uint32), ok.view(np.uint32)) and np.array_equal(host(vd), ov)
+    same = np.full(20000, 42, np.int32)                # every digit degenerate: all passes skipped
+    kd, vd = dev(same), dev(np.arange(20000, dtype=np.uint32))
+    tb.sort_by_key(kd, vd)
+    assert np.array_equal(host(vd), np.arange(20000, dtype=np.uint32))
+    ext = np.array([np.iinfo(np.int64).min, -1, 0, 1, np.iinfo(np.int64).max] * 700, np.int64)
+    kd = dev(ext)
+    tb.sort(kd)
+    assert np.array_equal(host(kd), np.sort(ext))
+
+
+def test_sort_bit_range(tb, port):
+    """testing/sort_by_key_variable_bits.cu: keys masked to few bits; and an explicit bit window."""
+    n = 30011
+    for bits in (1, 5, 8, 13, 24):
+        k = (dg.sort_keys_u32(n) & np.uint32((1 << bits) - 1)).astype(np.uint32)
+        v = np.arange(n, dtype=np.uint32)
+        kd, vd = dev(k), dev(v)
+        tb.sort_by_key(kd, vd)
+        ok, ov = port.sort_by_key(k, v)
+        assert np.array_equal(host(kd), ok) and np.array_equal(host(vd), ov), bits
+    k = dg.sort_keys_u32(n)
+    v = np.arange(n, dtype=np.uint32)
+    kd, vd = dev(k), dev(v)
+    tb.sort_by_key(kd, vd, begin_bit=8, end_bit=24)    # orders on bits 8..23 only, stably
+    order = np.argsort((k >> 8) & 0xFFFF, kind="stable")
+    assert np.array_equal(host(vd), v[order]) and np.array_equal(host(kd), k[order])
+
+
+@pytest.mark.parametrize("n", [0, 1, 2, 33, 4095, 4096, 4097, 8193, 65536 + 17, (1 << 20) + 3])
+def test_merge_sort_zip_by_first(tb, oracles, n):
+    """stable_sort(zip(u32 key, float value), get<0>(a) < get<0>(b)) on the comparison-sort route."""
+    k, v = dg.zip_sort_input(n)
+    k = (k >> np.uint32(18)).astype(np.uint32)         # 14-bit keys: ties everywhere
+    kd, vd = dev(k), dev(v)
+    tb.stable_sort_zip_by_first(kd, vd, method="merge")
+    kr, vr = dev(k), dev(v)
+    tb.stable_sort_zip_by_first(kr, vr, method="radix")
+    for o in oracles:
+        ok, ov = o.stable_sort_zip_by_first(k, v.view(np.uint32))
+        assert np.array_equal(host(kd), ok) and np.array_equal(host(vd).view(np.uint32), ov)
+        assert np.array_equal(host(kr), ok) and np.array_equal(host(vr).view(np.uint32), ov)
+
+
+def test_merge_sort_types(tb, port):
+    n = 50021
+    for dt in KEY_TYPES:
+        k = rand_of(dt, n, 55, small=True)
+        v = np.arange(n, dtype=np.uint64)
+        for desc in (False, True):
+            kd, vd = dev(k), dev(v)
+            tb.merge_sort_by_key(kd, vd, desc)
+            ok, ov = port.sort_by_key(k, v, desc)
+            assert np.array_equal(host(kd), ok) and np.array_equal(host(vd), ov), (dt, desc)
+            kd = dev(k)
+            tb.merge_sort_by_key(kd, None, desc)
+            assert np.array_equal(host(kd), ok)
+
+
+def test_golden_sorts(tb, golden):
+    for n in (1, 777, 12345):
+        v = np.arange(n, dtype=np.uint32)
+        kd, vd = dev(golden[f"sort_keys_in_{n}"]), dev(v)
+        tb.sort_by_key(kd, vd)
+        assert np.array_equal(host(kd), golden[f"sort_keys_out_{n}"]) and np.array_equal(host(vd), golden[f"sort_vals_out_{n}"])
+        kd, vd = dev(golden[f"sort64_keys_in_{n}"]), dev(v)
+        tb.sort_by_key(kd, vd)
+        assert np.array_equal(host(kd), golden[f"sort64_keys_out_{n}"]) and np.array_equal(host(vd), golden[f"sort64_vals_out_{n}"])
+        kd, vd = dev(golden[f"zip_keys_in_{n}"]), dev(golden[f"zip_vals_in_{n}"])
+        tb.stable_sort_zip_by_first(kd, vd)
+        assert np.array_equal(host(kd), golden[f"zip_keys_out_{n}"])
+        assert np.array_equal(host(vd).view(np.uint32), golden[f"zip_vals_out_{n}"])
+
+
+def test_full_size_sort_properties(tb):
+    """2^28 pairs: sorted, a permutation of the input (keys[i] == original[value[i]]), and stable
+    (values increase inside every run of equal keys)."""
+    n = 1 << 28
+    k0 = dev(dg.sort_keys_u32(n))
+    k = k0.clone()
+    v = torch.arange(n, dtype=torch.int32, device="cuda").view(torch.uint32)
+    tb.sort_by_key(k, v)
+    ki, vi = k.view(torch.int32), v.view(torch.int32)
+    flipped = ki ^ torch.tensor(-(1 << 31), dtype=torch.int32, device="cuda")      # unsigned order as signed
+    assert bool((flipped[1:] >= flipped[:-1]).all())
+    assert torch.equal(k0.view(torch.int32)[vi.long()], ki)
+    ties = ki[1:] == ki[:-1]
+    assert bool((vi[1:][ties] > vi[:-1][ties]).all())
+    assert int(vi.long().sum()) == n * (n - 1) // 2

@@ -18,7 +18,7 @@ PROTOTYPES = {
     "tb200_sm_arch": [],
     "tb200_workspace_status": [_vp, _vp, C.POINTER(C.c_uint)],
     "tb200_reduce": [_vp, _sz, _i, _i, _i, _vp, _vp, _vp, _szp, _vp],
-    "tb200_inclusive_scan": [_vp, _vp, _sz, _i, _i, _vp, _szp, _vp],
+    "tb200_inclusive_scan": [_vp, _vp, _sz, _i, _i, _vp, _vp, _szp, _vp],
     "tb200_exclusive_scan": [_vp, _vp, _sz, _i, _i, _vp, _vp, _szp, _vp],
     "tb200_sort_by_key": [_vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _vp, _szp, _vp],
     "tb200_copy_if": [_vp, _vp, _vp, _sz, _i, _i, _i, _ll, _ll, _vp, _vp, _szp, _vp],
@@ -28,6 +28,9 @@ PROTOTYPES = {
     "tb200_reduce_by_key": [_vp, _vp, _vp, _vp, _sz, _i, _i, _i, _vp, _vp, _szp, _vp],
     "tb200_merge_by_key": [_vp, _vp, _sz, _vp, _vp, _sz, _vp, _vp, _i, _i, _i, _vp, _szp, _vp],
     "tb200_merge_sort_by_key": [_vp, _vp, _vp, _vp, _sz, _i, _i, _i, _vp, _szp, _vp],
+    "tb200_lower_bound": [_vp, _sz, _vp, _sz, _vp, _i, _i, _vp],
+    "tb200_kernel_timing": [_i],
+    "tb200_kernel_timing_read": [_i, C.POINTER(C.c_int), C.POINTER(C.c_float), C.POINTER(C.c_int)],
 }
 
 _lib = None

@@ -107,11 +107,14 @@ def reduce(x, init=None, op="plus", acc_dtype=None):
 
 
 # ------------------------------------------------------------------------------------- scan
-def inclusive_scan(x, out=None, op="plus"):
-    """thrust::inclusive_scan(first, last, result, op); out may be x (in place).  Returns out."""
+def inclusive_scan(x, out=None, op="plus", init=None):
+    """thrust::inclusive_scan(first, last, result, op); out may be x (in place).  Returns out.
+    `init`, if given, is combined in front of the first element (the carry of a sharded scan)."""
     _require_cuda(x, out)
     out = torch.empty_like(x) if out is None else out
-    ws = _call_with_ws("scan", "tb200_inclusive_scan", _ptr(x), _ptr(out), x.numel(), DTYPE_CODE[x.dtype], OPS[op])
+    h_init = None if init is None else np.asarray(init, dtype=NP_OF[x.dtype])
+    ws = _call_with_ws("scan", "tb200_inclusive_scan", _ptr(x), _ptr(out), x.numel(), DTYPE_CODE[x.dtype], OPS[op],
+                       None if h_init is None else C.c_void_p(h_init.ctypes.data))
     _sync_and_check(ws, "inclusive_scan")
     return out
 

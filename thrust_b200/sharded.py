@@ -1,0 +1,211 @@
+"""Multi-GPU forms of the three paths that shard: reduce, scan and sort_by_key.
+
+One process per GPU (torch.distributed, NCCL over NVLink); each rank owns a contiguous slice of
+the global sequence, rank order being sequence order.  The reference has no multi-GPU path at all;
+the semantics here are "the result the single-GPU algorithm would give on the concatenation":
+
+  reduce       per-GPU single-pass reduce, then an all-reduce of one accumulator per GPU;
+  scan         per-GPU reduce -> all-gather of the G totals -> each GPU folds the totals of the
+               ranks before it into a carry -> per-GPU look-back scan seeded with that carry
+               (12 bytes of HBM traffic per 4-byte element instead of 8);
+  sort_by_key  per-GPU radix sort -> regular samples -> G-1 global splitters -> lower bounds cut
+               each sorted shard into G pieces -> all-to-all of keys and values over NVLink ->
+               each GPU merges the G sorted pieces it received, in source-rank order, with the
+               stable merge-path merge.  Equal keys all land on one GPU and keep (rank, index)
+               order, so the global result is the stable sort of the concatenation.
+
+The collectives move only what has to move: 8 bytes per GPU for reduce, 8*G for scan, the keys and
+values themselves for sort.  The compute steps go through an `ops` object: DeviceOps (the C-ABI
+kernels, the default and the only one shipped) or, in the CPU tests of this orchestration, a
+stand-in with the same methods.
+"""
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from . import api
+
+_NP_IDENTITY = {
+    "plus": lambda dt: np.zeros((), dt),
+    "min": lambda dt: np.array(np.finfo(dt).max if np.issubdtype(dt, np.floating) else np.iinfo(dt).max, dt),
+    "max": lambda dt: np.array(np.finfo(dt).min if np.issubdtype(dt, np.floating) else np.iinfo(dt).min, dt),
+}
+_NP_OP = {"plus": np.add, "min": np.minimum, "max": np.maximum}
+_REDUCE_OP = {"plus": dist.ReduceOp.SUM, "min": dist.ReduceOp.MIN, "max": dist.ReduceOp.MAX}
+
+# integer views NCCL and torch indexing are happy with (uint32/uint64 tensors support few torch ops)
+_SIGNED_VIEW = {torch.uint32: torch.int32, torch.uint64: torch.int64, torch.uint16: torch.int16}
+
+
+def _plumbing_view(t):
+    return t.view(_SIGNED_VIEW[t.dtype]) if t.dtype in _SIGNED_VIEW else t
+
+
+class DeviceOps:
+    """The product path: every compute step is a C-ABI call on CUDA tensors."""
+
+    def reduce(self, x, init, op):
+        return api.reduce(x, init, op)
+
+    def inclusive_scan(self, x, op, init):
+        return api.inclusive_scan(x, op=op, init=init)
+
+    def exclusive_scan(self, x, op, init):
+        return api.exclusive_scan(x, init=init, op=op)
+
+    def sort_by_key(self, keys, vals, descending):
+        if vals is None:
+            api.sort(keys, descending)
+        else:
+            api.sort_by_key(keys, vals, descending)
+
+    def merge_by_key(self, ka, kb, va, vb, descending):
+        return api.merge_by_key(ka, kb, va, vb, descending)
+
+    def lower_bound(self, sorted_keys, needles, descending):
+        import ctypes as C
+        lib = api._lib.load()
+        out = torch.empty(needles.numel(), dtype=torch.int64, device=sorted_keys.device)
+        rc = lib.tb200_lower_bound(api._ptr(sorted_keys), sorted_keys.numel(), api._ptr(needles), needles.numel(),
+                                   api._ptr(out), api.DTYPE_CODE[sorted_keys.dtype], int(descending), api._stream())
+        api._check(rc, "tb200_lower_bound")
+        return out
+
+
+def _world(group):
+    return dist.get_world_size(group), dist.get_rank(group)
+
+
+def _np_dtype(t):
+    return np.dtype(api.NP_OF[t.dtype])
+
+
+def sharded_reduce(x_local, init, op="plus", group=None, ops=None):
+    """thrust::reduce over the concatenation of every rank's x_local.  `init` is a numpy scalar
+    whose dtype is the accumulator type.  Every rank returns the same numpy scalar."""
+    ops = ops or DeviceOps()
+    init = np.asarray(init)
+    acc = init.dtype
+    partial = ops.reduce(x_local, _NP_IDENTITY[op](acc)[()], op)
+    t = torch.from_numpy(np.asarray(partial, dtype=acc).reshape(1).copy()).to(x_local.device)
+    dist.all_reduce(_plumbing_view(t), op=_REDUCE_OP[op], group=group)
+    total = t.cpu().numpy().astype(acc)[0]
+    with np.errstate(over="ignore"):
+        return _NP_OP[op](init, total).astype(acc)[()]
+
+
+def sharded_scan(x_local, op="plus", exclusive=False, init=None, group=None, ops=None):
+    """Inclusive or exclusive scan of the concatenation; returns this rank's slice of the result.
+    Accumulates in x_local's dtype, like the single-GPU scan."""
+    ops = ops or DeviceOps()
+    world, rank = _world(group)
+    dt = _np_dtype(x_local)
+    total = ops.reduce(x_local, _NP_IDENTITY[op](dt)[()], op)
+    mine = torch.from_numpy(np.asarray(total, dtype=dt).reshape(1).copy()).to(x_local.device)
+    gathered = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather([_plumbing_view(g) for g in gathered], _plumbing_view(mine), group=group)
+    totals = [g.cpu().numpy().astype(dt)[0] for g in gathered]
+    # carry = init (+) totals of the ranks before this one, folded left to right in the element type
+    carry = None if init is None else np.asarray(init, dtype=dt)[()]
+    with np.errstate(over="ignore"):
+        for r in range(rank):
+            carry = totals[r] if carry is None else _NP_OP[op](carry, totals[r]).astype(dt)[()]
+    if exclusive:
+        if carry is None:
+            carry = np.zeros((), dt)[()]
+        return ops.exclusive_scan(x_local, op, carry)
+    return ops.inclusive_scan(x_local, op, carry)
+
+
+def _exchange(pieces_send, send_counts, recv_counts, group):
+    """All-to-all of variable-sized pieces of one tensor.  pieces_send is the local tensor laid out
+    destination-major; returns the received tensor laid out source-major."""
+    world, rank = _world(group)
+    out = torch.empty(int(sum(recv_counts)), dtype=pieces_send.dtype, device=pieces_send.device)
+    if dist.get_backend(group) == "nccl":
+        dist.all_to_all_single(_plumbing_view(out), _plumbing_view(pieces_send), [int(c) for c in recv_counts],
+                               [int(c) for c in send_counts], group=group)
+        return out
+    # gloo has no all-to-all: pairwise send/recv (CPU tests of the orchestration only)
+    send_off = np.concatenate([[0], np.cumsum(send_counts)]).astype(np.int64)
+    recv_off = np.concatenate([[0], np.cumsum(recv_counts)]).astype(np.int64)
+    out[recv_off[rank]:recv_off[rank + 1]] = pieces_send[send_off[rank]:send_off[rank + 1]]
+    reqs = []
+    for peer in range(world):
+        if peer == rank:
+            continue
+        if send_counts[peer]:
+            reqs.append(dist.isend(_plumbing_view(pieces_send[send_off[peer]:send_off[peer + 1]]).contiguous(), peer, group=group))
+        if recv_counts[peer]:
+            reqs.append(dist.irecv(_plumbing_view(out[recv_off[peer]:recv_off[peer + 1]]), peer, group=group))
+    for r in reqs:
+        r.wait()
+    return out
+
+
+def choose_splitters(all_samples, world, descending=False):
+    """G-1 splitters from the gathered regular samples (a numpy array, any order): the elements at
+    every (len/G)-th position of the sorted sample."""
+    s = np.sort(all_samples, kind="stable")
+    if descending:
+        s = s[::-1]
+    if s.size == 0:
+        return s[:0]
+    pos = [(i * s.size) // world for i in range(1, world)]
+    return np.ascontiguousarray(s[pos])
+
+
+def sharded_sort_by_key(keys_local, vals_local=None, descending=False, group=None, ops=None, samples_per_rank=1024):
+    """Stable sort of the concatenation of every rank's (keys_local, vals_local).  Returns this
+    rank's slice (keys, vals) of the sorted sequence; slices are contiguous in rank order, sized by
+    the splitters (about 1/G of the data each for sampled splitters)."""
+    ops = ops or DeviceOps()
+    world, rank = _world(group)
+    dev = keys_local.device
+    n = keys_local.numel()
+    keys = keys_local.clone()
+    vals = None if vals_local is None else vals_local.clone()
+    ops.sort_by_key(keys, vals, descending)
+    if world == 1:
+        return keys, vals
+
+    # regular samples of the sorted shard -> identical splitters on every rank
+    s = min(samples_per_rank, n)
+    dt = _np_dtype(keys)
+    if s:
+        idx = torch.from_numpy(((np.arange(s, dtype=np.int64) * 2 + 1) * n // (2 * s))).to(dev)
+        mine = _plumbing_view(keys)[idx].cpu().numpy().view(dt)
+    else:
+        mine = np.empty(0, dt)
+    gathered = [None] * world
+    dist.all_gather_object(gathered, mine, group=group)
+    splitters = choose_splitters(np.concatenate(gathered), world, descending)
+    if splitters.size < world - 1:     # no data anywhere
+        return keys, vals
+
+    # cut the sorted shard at the splitters: piece d goes to rank d
+    cuts = ops.lower_bound(keys, torch.from_numpy(splitters.copy()).to(dev), descending).cpu().numpy().astype(np.int64)
+    bounds = np.concatenate([[0], cuts, [n]])
+    send_counts = np.diff(bounds)
+    counts_t = torch.from_numpy(send_counts.copy()).to(dev)
+    all_counts = [torch.empty_like(counts_t) for _ in range(world)]
+    dist.all_gather(all_counts, counts_t, group=group)
+    count_matrix = np.stack([c.cpu().numpy() for c in all_counts])      # [src][dst]
+    recv_counts = count_matrix[:, rank]
+
+    rk = _exchange(keys, send_counts, recv_counts, group)
+    rv = None if vals is None else _exchange(vals, send_counts, recv_counts, group)
+
+    # merge the G sorted runs received, pairwise in source-rank order (ties keep the lower rank first)
+    off = np.concatenate([[0], np.cumsum(recv_counts)]).astype(np.int64)
+    runs = [(rk[off[i]:off[i + 1]], None if rv is None else rv[off[i]:off[i + 1]]) for i in range(world)]
+    while len(runs) > 1:
+        nxt = []
+        for i in range(0, len(runs) - 1, 2):
+            (ka, va), (kb, vb) = runs[i], runs[i + 1]
+            nxt.append(ops.merge_by_key(ka.contiguous(), kb.contiguous(), None if va is None else va.contiguous(),
+                                        None if vb is None else vb.contiguous(), descending))
+        if len(runs) % 2:
+            nxt.append(runs[-1])
+        runs = nxt
+    return runs[0]
