@@ -320,13 +320,19 @@ def run_ours(args):
         # per rank: local sort (7) + lower_bound (1) + log2(G) merge rounds of (partition + merge) kernels
         launches_per_step = 7 + 1 + 2 * (world - 1)
 
-    for _ in range(args.warmup):
-        restore()
-        step()
-    barrier()
+    # the clock sampler runs from before the warm-up to after the timed steps, so that even a timed
+    # region of a few tens of milliseconds is covered by samples taken under the same load
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+        time.sleep(0.3)
+    for _ in range(max(args.warmup, 3)):
+        restore()
+        step()
+    t_load = time.perf_counter()
+    while time.perf_counter() - t_load < 1.0:      # keep the GPU under this load for a second of samples
+        restore()
+        step()
     barrier()
     t_wall = time.perf_counter()
     times = time_calls(torch, step, args.steps, restore)
