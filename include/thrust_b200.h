@@ -154,6 +154,30 @@ int tb200_lower_bound(const void* d_sorted, size_t n, const void* d_needles, siz
 int tb200_kernel_timing(int enable);
 int tb200_kernel_timing_read(int capacity, int* h_kernel_ids, float* h_ms, int* h_count);
 
+/* Inclusive scan for callers that cannot allocate device memory.  (No counterpart in the
+ * reference, whose every algorithm obtains temporary storage through the policy's allocator.)
+ *
+ * Who needs it: a caller that may not call cudaMalloc at the point where it needs a scan -- inside
+ * a stream-ordered pool's callback, in a latency-critical loop where cudaMalloc's device-wide
+ * synchronisation is not acceptable, in a plug-in that receives buffers but no allocator, or when
+ * its own data has already claimed all device memory.  The other entry points make such a caller
+ * bring the scratch; this one brings its own: a 256 KiB array in the library's device data
+ * segment, which every GPU that loads the library holds until the process exits.
+ *
+ * Same arguments and result as tb200_inclusive_scan minus the workspace pair.  Limit: the tile
+ * descriptors must fit the array, i.e. n <= about 2^27 elements for I32/U32/F32 and n <= about
+ * 2^24 for I64/U64/F64; beyond that the call does nothing and returns
+ * TB200_ERR_EXCEEDS_STATIC_SCRATCH.  It calls no cudaMalloc, cudaFree or other allocating routine.
+ *
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
+ * that device current) and remembers it; make that first call before starting any stream capture.
+ * All calls on a device share the one array.  Each call clears what it needs before use, so calls
+ * issued one after another on a stream are independent, but two calls whose kernels can overlap on
+ * the GPU (different streams, different host threads) race on it: serialise them. */
+#define TB200_ERR_EXCEEDS_STATIC_SCRATCH 100001
+int tb200_inclusive_scan_static(const void* d_in, void* d_out, size_t n, int t, int op,
+                                const void* h_init, tb200_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -29,6 +29,7 @@ PROTOTYPES = {
     "tb200_merge_by_key": [_vp, _vp, _sz, _vp, _vp, _sz, _vp, _vp, _i, _i, _i, _vp, _szp, _vp],
     "tb200_merge_sort_by_key": [_vp, _vp, _vp, _vp, _sz, _i, _i, _i, _vp, _szp, _vp],
     "tb200_lower_bound": [_vp, _sz, _vp, _sz, _vp, _i, _i, _vp],
+    "tb200_inclusive_scan_static": [_vp, _vp, _sz, _i, _i, _vp, _vp],
     "tb200_kernel_timing": [_i],
     "tb200_kernel_timing_read": [_i, C.POINTER(C.c_int), C.POINTER(C.c_float), C.POINTER(C.c_int)],
 }
