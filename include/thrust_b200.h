@@ -165,8 +165,8 @@ int tb200_kernel_timing_read(int capacity, int* h_kernel_ids, float* h_ms, int* 
  * segment, which every GPU that loads the library holds until the process exits.
  *
  * Same arguments and result as tb200_inclusive_scan minus the workspace pair.  Limit: the tile
- * descriptors must fit the array, i.e. n <= about 2^27 elements for I32/U32/F32 and n <= about
- * 2^24 for I64/U64/F64; beyond that the call does nothing and returns
+ * descriptors must fit the array, i.e. n <= about 2^28 elements for I32/U32/F32 and n <= about
+ * 2^25 for I64/U64/F64; beyond that the call does nothing and returns
  * TB200_ERR_EXCEEDS_STATIC_SCRATCH.  It calls no cudaMalloc, cudaFree or other allocating routine.
  *
  * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with

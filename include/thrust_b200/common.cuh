@@ -8,10 +8,21 @@
 #include <stdint.h>
 #include <stddef.h>
 #include <type_traits>
+#include <string.h>
 
 namespace tb200 {
 
 constexpr int WARP_THREADS = 32;
+
+// Shared-memory storage for element types that are not trivially constructible (tuples, user
+// structs): raw bytes viewed as T, never constructed.
+#define TB200_SHARED_ARRAY(T, name, count) \
+  __shared__ __align__(16) unsigned char name##_raw[sizeof(T) * (count)]; \
+  T* name = reinterpret_cast<T*>(name##_raw)
+#define TB200_SHARED_OBJECT(T, name) \
+  __shared__ __align__(16) unsigned char name##_raw[sizeof(T)]; \
+  T& name = *reinterpret_cast<T*>(name##_raw)
+
 constexpr unsigned FULL_MASK = 0xffffffffu;
 
 // Error codes a kernel may leave in the workspace status word (see ws_header).
@@ -93,14 +104,32 @@ struct less_op { template <class T> __host__ __device__ bool operator()(const T&
 struct greater_op { template <class T> __host__ __device__ bool operator()(const T& a, const T& b) const { return b < a; } };
 
 // Predicate of the C ABI: kind 0: x % a == b, 1: x < a, 2: x >= a, 3: x != a.
+// make() picks cheaper forms of the modulo test where they give the same answer: a mask when a is
+// a power of two and b is 0 (true for negative x too in two's complement), 32-bit division when
+// the operands fit; the 64-bit division remains the general case.
 struct abi_pred {
   int kind; long long a, b;
+  static abi_pred make(int kind, long long a, long long b) {
+    abi_pred p; p.kind = kind; p.a = a; p.b = b;
+    if (kind == 0) {
+      if (b == 0 && a > 0 && (a & (a - 1)) == 0) { p.kind = 4; p.a = a - 1; }
+      else if (a > 0 && a <= 0x7fffffffll && b >= 0 && b <= 0x7fffffffll) p.kind = 5;
+    }
+    return p;
+  }
   template <class T> __host__ __device__ bool operator()(const T& x) const {
     switch (kind) {
       case 0: return (long long)x % a == b;
       case 1: return x < (T)a;
       case 2: return x >= (T)a;
-      default: return x != (T)a;
+      case 3: return x != (T)a;
+      case 4: return ((long long)x & a) == 0;
+      default:
+        if (sizeof(T) <= 4 && std::is_integral<T>::value) {
+          if (std::is_signed<T>::value) return (int)x % (int)a == (int)b;
+          return (unsigned)x % (unsigned)a == (unsigned)b;
+        }
+        return (long long)x % a == b;
     }
   }
 };
@@ -120,16 +149,19 @@ template <class T> struct opt {
 template <class T> __device__ __forceinline__ T shfl_generic(const T& x, int src_lane, int mode, int arg) {
   // mode 0: idx, 1: up, 2: down, 3: xor
   constexpr int W = (sizeof(T) + 3) / 4;
-  union { T t; unsigned w[W]; } in, out;
-  in.t = x;
+  unsigned in[W], out[W];
+  in[W - 1] = 0;
+  memcpy(in, &x, sizeof(T));
 #pragma unroll
   for (int i = 0; i < W; ++i) {
-    if (mode == 0) out.w[i] = __shfl_sync(FULL_MASK, in.w[i], src_lane);
-    else if (mode == 1) out.w[i] = __shfl_up_sync(FULL_MASK, in.w[i], arg);
-    else if (mode == 2) out.w[i] = __shfl_down_sync(FULL_MASK, in.w[i], arg);
-    else out.w[i] = __shfl_xor_sync(FULL_MASK, in.w[i], arg);
+    if (mode == 0) out[i] = __shfl_sync(FULL_MASK, in[i], src_lane);
+    else if (mode == 1) out[i] = __shfl_up_sync(FULL_MASK, in[i], arg);
+    else if (mode == 2) out[i] = __shfl_down_sync(FULL_MASK, in[i], arg);
+    else out[i] = __shfl_xor_sync(FULL_MASK, in[i], arg);
   }
-  return out.t;
+  T r;
+  memcpy(&r, out, sizeof(T));
+  return r;
 }
 template <class T> __device__ __forceinline__ T shfl_idx(const T& x, int lane) { return shfl_generic(x, lane, 0, 0); }
 template <class T> __device__ __forceinline__ T shfl_up(const T& x, int d) { return shfl_generic(x, 0, 1, d); }
@@ -217,12 +249,14 @@ template <class T> struct tile_state<T, true> {
   static size_t bytes(size_t tiles) { return align_up(tiles * 8, 256); }
   void bind(void* p, size_t) { words = static_cast<unsigned long long*>(p); }
   __device__ __forceinline__ void publish(size_t tile, unsigned status, const T& v) const {
-    union { T t; unsigned u; } c; c.t = v;
-    st_relaxed_u64(words + tile, ((unsigned long long)status << 32) | c.u);
+    unsigned u;
+    memcpy(&u, &v, 4);
+    st_relaxed_u64(words + tile, ((unsigned long long)status << 32) | u);
   }
   __device__ __forceinline__ unsigned poll(size_t tile, T& v) const {
     unsigned long long w = ld_relaxed_u64(words + tile);
-    union { T t; unsigned u; } c; c.u = (unsigned)w; v = c.t;
+    unsigned u = (unsigned)w;
+    memcpy(&v, &u, 4);
     return (unsigned)(w >> 32);
   }
 };

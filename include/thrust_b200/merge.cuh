@@ -92,8 +92,8 @@ template <class KeyItA, class KeyItB, class ValItA, class ValItB, class KeyOutIt
 __global__ void __launch_bounds__(MERGE_BLOCK)
 merge_kernel(KeyItA ka, KeyItB kb, ValItA va, ValItB vb, KeyOutIt ko, ValOutIt vo, merge_geometry g, Comp comp, const size_t* a_split) {
   constexpr int TILE = MERGE_BLOCK * IPT;
-  __shared__ K s_key[TILE + 1];
-  __shared__ V s_val[HAS_V ? TILE : 1];
+  TB200_SHARED_ARRAY(K, s_key, TILE + 1);
+  TB200_SHARED_ARRAY(V, s_val, HAS_V ? TILE : 1);
   const size_t t = blockIdx.x;
   size_t a0p, alen, b0p, blen, pair_out, local;
   g.locate<TILE>(t, a0p, alen, b0p, blen, pair_out, local);
@@ -202,7 +202,7 @@ template <class KeyIt, class ValIt, class KeyOutIt, class ValOutIt, class K, cla
 __global__ void __launch_bounds__(MERGE_BLOCK)
 block_sort_kernel(KeyIt keys, ValIt vals, KeyOutIt keys_out, ValOutIt vals_out, size_t n, Comp comp) {
   constexpr int TILE = MERGE_BLOCK * IPT;
-  __shared__ K s_key[TILE + 1];
+  TB200_SHARED_ARRAY(K, s_key, TILE + 1);
   __shared__ unsigned short s_idx[TILE + 1];
   const size_t base = (size_t)blockIdx.x * TILE;
   const unsigned tile_n = n - base < TILE ? (unsigned)(n - base) : (unsigned)TILE;

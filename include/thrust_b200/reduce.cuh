@@ -36,7 +36,7 @@ template <class InIt, class AccT, class Op, int VEC>
 __global__ void __launch_bounds__(REDUCE_BLOCK)
 reduce_kernel(InIt in, size_t n, AccT init, Op op, AccT* partials, unsigned* partial_has,
               unsigned* ticket, AccT* out) {
-  __shared__ opt<AccT> smem[32];
+  TB200_SHARED_ARRAY(opt<AccT>, smem, 32);
   __shared__ bool is_last;
   const size_t tid = (size_t)blockIdx.x * REDUCE_BLOCK + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * REDUCE_BLOCK;

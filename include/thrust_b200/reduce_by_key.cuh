@@ -44,9 +44,10 @@ reduce_by_key_kernel(KeyIt keys, ValIt vals, KeyOutIt keys_out, ValOutIt vals_ou
   constexpr int WCHUNK = 32 * IPT;
   constexpr int TILE = RBK_BLOCK * IPT;
   __shared__ unsigned s_tile;
-  __shared__ tile_prefix_smem<P, NWARPS> sm;
-  __shared__ K stage_k[TILE];
-  __shared__ V stage_v[TILE];
+  using prefix_smem_t = tile_prefix_smem<P, NWARPS>;
+  TB200_SHARED_OBJECT(prefix_smem_t, sm);
+  TB200_SHARED_ARRAY(K, stage_k, TILE);
+  TB200_SHARED_ARRAY(V, stage_v, TILE);
 
   if (threadIdx.x == 0) s_tile = atomicAdd(&hdr->ticket, 1u);
   __syncthreads();

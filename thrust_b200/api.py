@@ -146,19 +146,20 @@ def _sort_impl(keys, vals, descending, begin_bit, end_bit, sync=True):
         _sync_and_check(ws, "sort")
 
 
-def sort(keys, descending=False):
-    """thrust::sort / thrust::stable_sort(first, last[, greater]) in place."""
-    _sort_impl(keys, None, descending, 0, None)
+def sort(keys, descending=False, sync=True):
+    """thrust::sort / thrust::stable_sort(first, last[, greater]) in place.  sync=False only
+    enqueues the work (for callers that chain several calls on one stream)."""
+    _sort_impl(keys, None, descending, 0, None, sync)
     return keys
 
 
 stable_sort = sort
 
 
-def sort_by_key(keys, vals, descending=False, begin_bit=0, end_bit=None):
+def sort_by_key(keys, vals, descending=False, begin_bit=0, end_bit=None, sync=True):
     """thrust::sort_by_key / stable_sort_by_key(keys_first, keys_last, values_first[, greater]) in
     place; stable."""
-    _sort_impl(keys, vals, descending, begin_bit, end_bit)
+    _sort_impl(keys, vals, descending, begin_bit, end_bit, sync)
     return keys, vals
 
 
@@ -241,7 +242,7 @@ def reduce_by_key(keys, vals, op="plus"):
 
 
 # ------------------------------------------------------------------------------------- merge
-def merge_by_key(keys_a, keys_b, vals_a=None, vals_b=None, descending=False):
+def merge_by_key(keys_a, keys_b, vals_a=None, vals_b=None, descending=False, sync=True):
     """thrust::merge_by_key(A, B, payload A, payload B, keys_out, payload_out[, greater]); with no
     payloads it is thrust::merge.  Returns (keys_out, payload_out or None)."""
     _require_cuda(keys_a, keys_b, vals_a, vals_b)
@@ -253,7 +254,8 @@ def merge_by_key(keys_a, keys_b, vals_a=None, vals_b=None, descending=False):
     vb = 0 if vals_a is None else vals_a.element_size()
     ws = _call_with_ws("merge", "tb200_merge_by_key", _ptr(keys_a), _ptr(vals_a), na, _ptr(keys_b), _ptr(vals_b), nb, _ptr(ko),
                        _ptr(vo), DTYPE_CODE[keys_a.dtype], vb, int(descending))
-    _sync_and_check(ws, "merge_by_key")
+    if sync:
+        _sync_and_check(ws, "merge_by_key")
     return ko, vo
 
 

@@ -16,7 +16,7 @@ TB200_API int tb200_partition(void* d_data, size_t n, int t, int pred, long long
     if (workspace_gate(d_ws, ws_bytes, sel + tb200::align_up(n * sizeof(T), 256), rc)) return rc;
     if (n && !d_data) return ERR_INVALID;
     T* scratch = reinterpret_cast<T*>(static_cast<char*>(d_ws) + sel);
-    abi_pred p{pred, a, b};
+    abi_pred p = abi_pred::make(pred, a, b);
     return (int)tb200::partition_inplace_async(static_cast<T*>(d_data), scratch, n, p, d_count, d_ws, stream);
   });
 }

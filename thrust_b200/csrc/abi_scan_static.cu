@@ -14,7 +14,7 @@ using namespace tb200_abi;
 
 namespace {
 
-// 256 KiB: the tile descriptors of up to 2^27 four-byte elements or 2^24 eight-byte elements.
+// 256 KiB: the tile descriptors of up to about 2^28 four-byte elements or 2^25 eight-byte elements.
 constexpr size_t STATIC_SCRATCH_BYTES = 256 * 1024;
 static __device__ __align__(256) unsigned char g_scan_scratch[STATIC_SCRATCH_BYTES];
 

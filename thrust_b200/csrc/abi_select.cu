@@ -32,7 +32,7 @@ int select_entry(const void* in, const void* stencil, void* out_sel, void* out_r
     int rc;
     if (workspace_gate(d_ws, ws_bytes, tb200::select_workspace_bytes<T>(n), rc)) return rc;
     if (n && (!in || !out_sel || (REJ && !out_rej))) return ERR_INVALID;
-    abi_pred p{pred, a, b};
+    abi_pred p = abi_pred::make(pred, a, b);
     return select_pred<T, REJ>(in, stencil, stencil_t, out_sel, out_rej, n, p, d_count, d_ws, stream);
   });
 }

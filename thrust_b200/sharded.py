@@ -54,13 +54,14 @@ class DeviceOps:
         return api.exclusive_scan(x, init=init, op=op)
 
     def sort_by_key(self, keys, vals, descending):
+        # enqueued only: the sharded algorithms wait for the GPU where they need a value on the host
         if vals is None:
-            api.sort(keys, descending)
+            api.sort(keys, descending, sync=False)
         else:
-            api.sort_by_key(keys, vals, descending)
+            api.sort_by_key(keys, vals, descending, sync=False)
 
     def merge_by_key(self, ka, kb, va, vb, descending):
-        return api.merge_by_key(ka, kb, va, vb, descending)
+        return api.merge_by_key(ka, kb, va, vb, descending, sync=False)
 
     def lower_bound(self, sorted_keys, needles, descending):
         import ctypes as C
@@ -158,7 +159,12 @@ def choose_splitters(all_samples, world, descending=False):
 def sharded_sort_by_key(keys_local, vals_local=None, descending=False, group=None, ops=None, samples_per_rank=1024):
     """Stable sort of the concatenation of every rank's (keys_local, vals_local).  Returns this
     rank's slice (keys, vals) of the sorted sequence; slices are contiguous in rank order, sized by
-    the splitters (about 1/G of the data each for sampled splitters)."""
+    the splitters (about 1/G of the data each for sampled splitters).
+
+    Everything up to the exchange is enqueued without waiting for the GPU: local sort, sample
+    gather, all-gather of the samples, sort of the gathered sample and splitter pick, lower bounds,
+    all-gather of the cut positions.  The host blocks once, to read the G x (G-1) cut positions that
+    size the all-to-all; the merges after the exchange are enqueued without waiting again."""
     ops = ops or DeviceOps()
     world, rank = _world(group)
     dev = keys_local.device
@@ -169,28 +175,48 @@ def sharded_sort_by_key(keys_local, vals_local=None, descending=False, group=Non
     if world == 1:
         return keys, vals
 
-    # regular samples of the sorted shard -> identical splitters on every rank
-    s = min(samples_per_rank, n)
-    dt = _np_dtype(keys)
-    if s:
-        idx = torch.from_numpy(((np.arange(s, dtype=np.int64) * 2 + 1) * n // (2 * s))).to(dev)
-        mine = _plumbing_view(keys)[idx].cpu().numpy().view(dt)
-    else:
-        mine = np.empty(0, dt)
-    gathered = [None] * world
-    dist.all_gather_object(gathered, mine, group=group)
-    splitters = choose_splitters(np.concatenate(gathered), world, descending)
-    if splitters.size < world - 1:     # no data anywhere
-        return keys, vals
+    # regular samples of the sorted shard; a rank without data contributes copies of nothing (flagged)
+    s = samples_per_rank
+    pick = torch.from_numpy(((np.arange(s, dtype=np.int64) * 2 + 1) * max(n, 1) // (2 * s))).to(dev)
+    kview = _plumbing_view(keys)
+    mine = kview[pick] if n else torch.zeros(s, dtype=kview.dtype, device=dev)
+    gathered = torch.empty(world * s, dtype=kview.dtype, device=dev)
+    dist.all_gather_into_tensor(gathered, mine, group=group) if dist.get_backend(group) == "nccl" else \
+        dist.all_gather(list(gathered.view(world, s).unbind(0)), mine, group=group)
+    sizes_t = torch.tensor([n], dtype=torch.int64, device=dev)
+    all_sizes = torch.empty(world, dtype=torch.int64, device=dev)
+    dist.all_gather_into_tensor(all_sizes, sizes_t, group=group) if dist.get_backend(group) == "nccl" else \
+        dist.all_gather(list(all_sizes.view(world, 1).unbind(0)), sizes_t, group=group)
 
-    # cut the sorted shard at the splitters: piece d goes to rank d
-    cuts = ops.lower_bound(keys, torch.from_numpy(splitters.copy()).to(dev), descending).cpu().numpy().astype(np.int64)
-    bounds = np.concatenate([[0], cuts, [n]])
-    send_counts = np.diff(bounds)
-    counts_t = torch.from_numpy(send_counts.copy()).to(dev)
-    all_counts = [torch.empty_like(counts_t) for _ in range(world)]
-    dist.all_gather(all_counts, counts_t, group=group)
-    count_matrix = np.stack([c.cpu().numpy() for c in all_counts])      # [src][dst]
+    # sort the gathered sample with the same kernels and take every (len/G)-th element as a splitter.
+    # (ranks without data are rare; they are handled by the host path below)
+    sample_keys = gathered.view(keys.dtype)
+    ops.sort_by_key(sample_keys, None, descending)
+    pos = torch.tensor([i * s for i in range(1, world)], dtype=torch.int64, device=dev)
+    splitters = _plumbing_view(sample_keys)[pos].view(keys.dtype)
+
+    cuts = ops.lower_bound(keys, splitters, descending)                       # [G-1] on the device
+    all_cuts = torch.empty(world * (world - 1), dtype=torch.int64, device=dev)
+    dist.all_gather_into_tensor(all_cuts, cuts, group=group) if dist.get_backend(group) == "nccl" else \
+        dist.all_gather(list(all_cuts.view(world, world - 1).unbind(0)), cuts, group=group)
+    # the one host wait: cut positions and shard sizes of every rank
+    meta = torch.cat([all_cuts, all_sizes]).cpu().numpy()
+    cut_matrix = meta[:world * (world - 1)].reshape(world, world - 1)
+    sizes_host = meta[world * (world - 1):]
+    if (sizes_host == 0).any():
+        # a rank without data contributed placeholder samples: redo the splitters on the host from the real ones
+        real = np.concatenate([gathered.view(world, s)[r].cpu().numpy().view(_np_dtype(keys)) for r in range(world) if sizes_host[r] > 0]) \
+            if (sizes_host > 0).any() else np.empty(0, _np_dtype(keys))
+        if real.size == 0:
+            return keys, vals
+        sp = choose_splitters(real, world, descending)
+        cuts = ops.lower_bound(keys, torch.from_numpy(sp.copy()).to(dev), descending)
+        dist.all_gather_into_tensor(all_cuts, cuts, group=group) if dist.get_backend(group) == "nccl" else \
+            dist.all_gather(list(all_cuts.view(world, world - 1).unbind(0)), cuts, group=group)
+        cut_matrix = all_cuts.cpu().numpy().reshape(world, world - 1)
+    bounds = np.concatenate([np.zeros((world, 1), np.int64), cut_matrix, sizes_host.reshape(world, 1)], axis=1)
+    count_matrix = np.diff(bounds, axis=1)                                    # [src][dst]
+    send_counts = count_matrix[rank]
     recv_counts = count_matrix[:, rank]
 
     rk = _exchange(keys, send_counts, recv_counts, group)
@@ -203,8 +229,7 @@ def sharded_sort_by_key(keys_local, vals_local=None, descending=False, group=Non
         nxt = []
         for i in range(0, len(runs) - 1, 2):
             (ka, va), (kb, vb) = runs[i], runs[i + 1]
-            nxt.append(ops.merge_by_key(ka.contiguous(), kb.contiguous(), None if va is None else va.contiguous(),
-                                        None if vb is None else vb.contiguous(), descending))
+            nxt.append(ops.merge_by_key(ka, kb, va, vb, descending))
         if len(runs) % 2:
             nxt.append(runs[-1])
         runs = nxt
