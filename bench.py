@@ -311,12 +311,15 @@ def run_ours(args):
         launches_per_step = 2 + 4 + 1     # histogram, bucket-base scan, four onesweep passes, copy-back check
     else:
         out = {}
+        k, v = torch.empty_like(k0), torch.empty_like(v0)
 
         def restore():
-            pass
+            k.copy_(k0)
+            v.copy_(v0)
 
         def step():
-            out["k"], out["v"] = sharded.sharded_sort_by_key(k0, v0)
+            # like thrust::sort_by_key, the sharded sort may consume its input
+            out["k"], out["v"] = sharded.sharded_sort_by_key(k, v, consume_input=True)
         # per rank: local sort (7) + lower_bound (1) + log2(G) merge rounds of (partition + merge) kernels
         launches_per_step = 7 + 1 + 2 * (world - 1)
 
@@ -383,13 +386,16 @@ def run_ours(args):
         d2h = 8 * n_local
     else:
         dk, dv = torch.empty_like(k0), torch.empty_like(v0)
+        # this rank's slice of the result is about n_local long; leave room for splitter imbalance
+        h_res_k = torch.empty(2 * n_local, dtype=h_keys.dtype).pin_memory()
+        h_res_v = torch.empty(2 * n_local, dtype=h_vals.dtype).pin_memory()
 
         def e2e_step():
             dk.copy_(h_keys, non_blocking=True)
             dv.copy_(h_vals, non_blocking=True)
-            rk, rv = sharded.sharded_sort_by_key(dk, dv)
-            rk.cpu()
-            rv.cpu()
+            rk, rv = sharded.sharded_sort_by_key(dk, dv, consume_input=True)
+            h_res_k[:rk.numel()].copy_(rk, non_blocking=True)
+            h_res_v[:rv.numel()].copy_(rv, non_blocking=True)
         d2h = 8 * n_local
     e2e_step()
     barrier()

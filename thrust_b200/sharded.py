@@ -156,7 +156,8 @@ def choose_splitters(all_samples, world, descending=False):
     return np.ascontiguousarray(s[pos])
 
 
-def sharded_sort_by_key(keys_local, vals_local=None, descending=False, group=None, ops=None, samples_per_rank=1024):
+def sharded_sort_by_key(keys_local, vals_local=None, descending=False, group=None, ops=None, samples_per_rank=1024, stage_marks=None,
+                        consume_input=False):
     """Stable sort of the concatenation of every rank's (keys_local, vals_local).  Returns this
     rank's slice (keys, vals) of the sorted sequence; slices are contiguous in rank order, sized by
     the splitters (about 1/G of the data each for sampled splitters).
@@ -164,14 +165,21 @@ def sharded_sort_by_key(keys_local, vals_local=None, descending=False, group=Non
     Everything up to the exchange is enqueued without waiting for the GPU: local sort, sample
     gather, all-gather of the samples, sort of the gathered sample and splitter pick, lower bounds,
     all-gather of the cut positions.  The host blocks once, to read the G x (G-1) cut positions that
-    size the all-to-all; the merges after the exchange are enqueued without waiting again."""
+    size the all-to-all; the merges after the exchange are enqueued without waiting again.
+    consume_input=True sorts the local shard in place first (thrust::sort_by_key itself is an in-place
+    algorithm) and so saves one copy of the shard; by default the inputs are left untouched.
+    stage_marks, if a list, receives (label, callable) pairs where the callable records a marker on
+    the current stream (the caller supplies what a marker is, e.g. a CUDA event)."""
     ops = ops or DeviceOps()
+    mark = (lambda label: stage_marks.append((label, stage_marks[0][1]()))) if stage_marks else (lambda label: None)
     world, rank = _world(group)
     dev = keys_local.device
     n = keys_local.numel()
-    keys = keys_local.clone()
-    vals = None if vals_local is None else vals_local.clone()
+    keys = keys_local if consume_input else keys_local.clone()
+    vals = None if vals_local is None else (vals_local if consume_input else vals_local.clone())
+    mark("copy")
     ops.sort_by_key(keys, vals, descending)
+    mark("local_sort")
     if world == 1:
         return keys, vals
 
@@ -199,6 +207,7 @@ def sharded_sort_by_key(keys_local, vals_local=None, descending=False, group=Non
     all_cuts = torch.empty(world * (world - 1), dtype=torch.int64, device=dev)
     dist.all_gather_into_tensor(all_cuts, cuts, group=group) if dist.get_backend(group) == "nccl" else \
         dist.all_gather(list(all_cuts.view(world, world - 1).unbind(0)), cuts, group=group)
+    mark("splitters")
     # the one host wait: cut positions and shard sizes of every rank
     meta = torch.cat([all_cuts, all_sizes]).cpu().numpy()
     cut_matrix = meta[:world * (world - 1)].reshape(world, world - 1)
@@ -219,8 +228,10 @@ def sharded_sort_by_key(keys_local, vals_local=None, descending=False, group=Non
     send_counts = count_matrix[rank]
     recv_counts = count_matrix[:, rank]
 
+    mark("host_wait")
     rk = _exchange(keys, send_counts, recv_counts, group)
     rv = None if vals is None else _exchange(vals, send_counts, recv_counts, group)
+    mark("exchange")
 
     # merge the G sorted runs received, pairwise in source-rank order (ties keep the lower rank first)
     off = np.concatenate([[0], np.cumsum(recv_counts)]).astype(np.int64)
@@ -233,4 +244,5 @@ def sharded_sort_by_key(keys_local, vals_local=None, descending=False, group=Non
         if len(runs) % 2:
             nxt.append(runs[-1])
         runs = nxt
+    mark("merge")
     return runs[0]
