@@ -34,7 +34,7 @@ template <class K, class V> struct rbk_tuning {
 };
 
 template <class KeyIt, class ValIt, class KeyOutIt, class ValOutIt, class K, class V, class Eq, class Op, class Off, int VEC, int IPT>
-__global__ void __launch_bounds__(RBK_BLOCK)
+__global__ void __launch_bounds__(RBK_BLOCK, 3)
 reduce_by_key_kernel(KeyIt keys, ValIt vals, KeyOutIt keys_out, ValOutIt vals_out, size_t n, Eq key_eq, Op op,
                      tile_state<rbk_pair<Off, V>> ts, ws_header* hdr, unsigned long long* d_count) {
   using P = rbk_pair<Off, V>;

@@ -34,7 +34,7 @@ template <class T> struct select_tuning {
 // KEEP_REJECTS: also write dropped items: mirrored == false -> out_rej[r], r = rank among dropped;
 //               mirrored == true -> out_sel[n - 1 - r].
 template <int MODE, bool KEEP_REJECTS, class InIt, class StIt, class SelIt, class RejIt, class T, class Pred, class Off, int VEC, int IPT>
-__global__ void __launch_bounds__(SELECT_BLOCK)
+__global__ void __launch_bounds__(SELECT_BLOCK, 4)
 select_kernel(InIt in, StIt stencil, SelIt out_sel, RejIt out_rej, size_t n, Pred pred, tile_state<Off> ts, ws_header* hdr,
               unsigned long long* d_count, bool mirrored) {
   constexpr int VPT = IPT / VEC;
