@@ -240,11 +240,23 @@ inline bool is_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p)
 // 2 = inclusive prefix (everything up to and including this tile) available.
 enum : unsigned { TILE_INVALID = 0, TILE_AGGREGATE = 1, TILE_INCLUSIVE = 2 };
 
-// 4-byte values travel with their status in one 64-bit word (one relaxed store, no fence);
-// anything else is written first and published by a release store of the status.
-template <class T, bool PACKED = (sizeof(T) == 4)> struct tile_state;
+// 4-byte values travel with their status in one 64-bit word and 8-byte values in one 128-bit word
+// (a single relaxed store / load each, no fence); anything else is written first and published by
+// a release store of the status.
+__device__ __forceinline__ void st_relaxed_b128(void* p, unsigned long long lo, unsigned long long hi) {
+  asm volatile("{\n\t.reg .b128 t;\n\tmov.b128 t, {%1, %2};\n\tst.relaxed.gpu.global.b128 [%0], t;\n\t}" ::"l"(p), "l"(lo), "l"(hi) : "memory");
+}
+__device__ __forceinline__ void ld_relaxed_b128(const void* p, unsigned long long& lo, unsigned long long& hi) {
+  asm volatile("{\n\t.reg .b128 t;\n\tld.relaxed.gpu.global.b128 t, [%2];\n\tmov.b128 {%0, %1}, t;\n\t}" : "=l"(lo), "=l"(hi) : "l"(p) : "memory");
+}
 
-template <class T> struct tile_state<T, true> {
+template <class T> struct tile_state_mode {
+  static constexpr int value = (sizeof(T) == 4 && std::is_trivially_copyable<T>::value) ? 1
+                             : (sizeof(T) == 8 && std::is_trivially_copyable<T>::value) ? 2 : 0;
+};
+template <class T, int MODE = tile_state_mode<T>::value> struct tile_state;
+
+template <class T> struct tile_state<T, 1> {
   unsigned long long* words;
   static size_t bytes(size_t tiles) { return align_up(tiles * 8, 256); }
   void bind(void* p, size_t) { words = static_cast<unsigned long long*>(p); }
@@ -261,7 +273,24 @@ template <class T> struct tile_state<T, true> {
   }
 };
 
-template <class T> struct tile_state<T, false> {
+template <class T> struct tile_state<T, 2> {
+  unsigned long long* words;   // [tile][2]: value bits, status
+  static size_t bytes(size_t tiles) { return align_up(tiles * 16, 256); }
+  void bind(void* p, size_t) { words = static_cast<unsigned long long*>(p); }
+  __device__ __forceinline__ void publish(size_t tile, unsigned status, const T& v) const {
+    unsigned long long u;
+    memcpy(&u, &v, 8);
+    st_relaxed_b128(words + 2 * tile, u, (unsigned long long)status);
+  }
+  __device__ __forceinline__ unsigned poll(size_t tile, T& v) const {
+    unsigned long long u, st;
+    ld_relaxed_b128(words + 2 * tile, u, st);
+    memcpy(&v, &u, 8);
+    return (unsigned)st;
+  }
+};
+
+template <class T> struct tile_state<T, 0> {
   unsigned* status; T* agg; T* inc;
   static size_t slot() { return (sizeof(T) + 15) / 16 * 16; }
   static size_t bytes(size_t tiles) { return align_up(tiles * 4, 256) + 2 * align_up(tiles * sizeof(T), 256); }

@@ -256,24 +256,6 @@ __device__ __forceinline__ void onesweep_tile(const UK* __restrict__ src, UK* __
 #pragma unroll
     for (int i = 0; i < IPT; ++i) val[i] = (FULL || wofs + i * 32 < tile_n) ? __ldcs(vs + i * 32) : (UV)0;
   }
-#ifdef TB200_ONESWEEP_COMBINED
-  if constexpr (HAS_V) {
-#pragma unroll
-    for (int i = 0; i < IPT; ++i) stage_v[pd[i]] = val[i];
-  }
-  __syncthreads();
-  // consecutive threads take consecutive staged slots, so each bucket's run is written contiguously
-#pragma unroll
-  for (int i = 0; i < IPT; ++i) {
-    unsigned j = threadIdx.x + i * ONESWEEP_BLOCK;
-    if (FULL || j < tile_n) {
-      UK k = stage_k[j];
-      const unsigned o = s_goff[key_digit<IS_FLOAT>(k, shift, dmask)] + j;
-      dst[o] = k;
-      if constexpr (HAS_V) vdst[o] = stage_v[j];
-    }
-  }
-#else
   __syncthreads();
   // consecutive threads take consecutive staged slots, so each bucket's run is written contiguously
 #pragma unroll
@@ -294,7 +276,6 @@ __device__ __forceinline__ void onesweep_tile(const UK* __restrict__ src, UK* __
       if (FULL || j < tile_n) vdst[s_goff[key_digit<IS_FLOAT>(stage_k[j], shift, dmask)] + j] = stage_v[j];
     }
   }
-#endif
 }
 
 template <class UK, class UV, bool HAS_V, bool IS_FLOAT, class LB, int IPT>

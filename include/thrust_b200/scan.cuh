@@ -23,7 +23,7 @@ template <class T> struct scan_tuning {
 };
 
 template <class InIt, class OutIt, class T, class Op, bool INCLUSIVE, int VEC, int IPT>
-__global__ void __launch_bounds__(SCAN_BLOCK)
+__global__ void __launch_bounds__(SCAN_BLOCK, 4)
 scan_kernel(InIt in, OutIt out, size_t n, T init, bool has_init, Op op, tile_state<T> ts, ws_header* hdr) {
   constexpr int VPT = IPT / VEC;
   constexpr int NWARPS = SCAN_BLOCK / 32;
