@@ -17,8 +17,8 @@ value = original index).  Rank 0 prints ONE JSON line:
   others       the remaining hot-path algorithms at their benchmark sizes (N=1 only).
 
 With N > 1 (torchrun, one rank per GPU) the same 2^28 pairs are split across the ranks and sorted
-by thrust_b200.sharded.sharded_sort_by_key: per-GPU radix sort, sampled splitters, NCCL all-to-all
-over NVLink, per-GPU merge of the received runs ("scaling": "strong").  `--impl reference` times the
+by thrust_b200.sharded.sharded_sort_by_key: per-GPU radix sort, sampled splitters, then per-GPU
+merges that read the pieces they need directly from the peers' memory over NVLink ("scaling": "strong").  `--impl reference` times the
 reference's own CPU implementation (OpenMP backend) on the host cores instead.
 """
 import argparse
@@ -320,8 +320,8 @@ def run_ours(args):
         def step():
             # like thrust::sort_by_key, the sharded sort may consume its input
             out["k"], out["v"] = sharded.sharded_sort_by_key(k, v, consume_input=True)
-        # per rank: local sort (7) + lower_bound (1) + log2(G) merge rounds of (partition + merge) kernels
-        launches_per_step = 7 + 1 + 2 * (world - 1)
+        # per rank: local sort (7) + sample sort (7) + lower_bound (1) + G-1 merges of (partition + merge) kernels
+        launches_per_step = 7 + 7 + 1 + 2 * (world - 1)
 
     # the clock sampler runs from before the warm-up to after the timed steps, so that even a timed
     # region of a few tens of milliseconds is covered by samples taken under the same load
@@ -414,7 +414,7 @@ def run_ours(args):
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u32", "data": "synthetic",
         "config": {"workload": WORKLOAD, "n": N_KEYS, "per_gpu": n_local,
                    "l2": "2 GiB of input per step (> 126 MB L2); the pristine input is restored by a 2 GiB device copy between timed steps",
-                   "parallelism": "1 GPU" if world == 1 else "%d GPUs: local radix sort + sampled splitters + NCCL all-to-all + local merge" % world},
+                   "parallelism": "1 GPU" if world == 1 else "%d GPUs: local radix sort + sampled splitters + merges that read the peers' shards over NVLink (CUDA IPC)" % world},
         "roofline": roofline, "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
         "wall_s_timed_region": t_wall,
         "sort_roofline": {"algorithmic_bytes_per_key": 68, "achieved_gbs": 68.0 * N_KEYS / ms / 1e6, "frac_of_hbm_peak": 68.0 * N_KEYS / ms / 1e6 / peak / world},

@@ -178,6 +178,21 @@ int tb200_kernel_timing_read(int capacity, int* h_kernel_ids, float* h_ms, int* 
 int tb200_inclusive_scan_static(const void* d_in, void* d_out, size_t n, int t, int op,
                                 const void* h_init, tb200_stream_t stream);
 
+/* Sharing device buffers between the ranks of a one-process-per-GPU job, so that a kernel on one
+ * GPU reads another GPU's buffer directly over NVLink with ordinary loads (the multi-GPU sort
+ * merges the runs it needs straight out of its peers' memory instead of copying them first).
+ * No counterpart in the reference, which has no multi-GPU path.
+ *   tb200_ipc_export   fills a 64-byte handle and the offset of d_ptr inside its allocation
+ *                      (cudaIpcGetMemHandle); send both to the peer process by any means;
+ *   tb200_ipc_open     maps the peer's allocation into this process (once per handle; later calls
+ *                      reuse the mapping) and returns the device pointer of the same bytes;
+ *   tb200_ipc_close_all unmaps everything opened so far.
+ * The exporting process must keep the buffer allocated while peers use it, and the two sides
+ * order their accesses themselves (a collective or a stream wait between writer and reader). */
+int tb200_ipc_export(const void* d_ptr, void* h_handle64, size_t* h_offset);
+int tb200_ipc_open(const void* h_handle64, size_t offset, void** d_ptr_out);
+int tb200_ipc_close_all(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -34,16 +34,20 @@ def _worker(rank, world, port, out_dir):
         for case, keys in (("uniform", dg.sort_keys_u32(n_total)), ("ties", (dg.sort_keys_u32(n_total) >> np.uint32(22)).astype(np.uint32)),
                            ("u64", dg.sort_keys_u64_40bit(n_total))):
             vals = np.arange(n_total, dtype=np.uint32)
-            k, v = sharded.sharded_sort_by_key(dev(keys[lo:hi]), dev(vals[lo:hi]))
-            np.save(os.path.join(out_dir, f"{case}_k{rank}.npy"), k.cpu().numpy())
-            np.save(os.path.join(out_dir, f"{case}_v{rank}.npy"), v.cpu().numpy())
-            dist.barrier()
-            if rank == 0:
-                kk = np.concatenate([np.load(os.path.join(out_dir, f"{case}_k{r}.npy")) for r in range(world)])
-                vv = np.concatenate([np.load(os.path.join(out_dir, f"{case}_v{r}.npy")) for r in range(world)])
-                wk, wv = o.sort_by_key(keys, vals)
-                assert np.array_equal(kk, wk) and np.array_equal(vv, wv), case
-            dist.barrier()
+            # "peer": merges read the pieces straight out of the other GPUs' memory (CUDA IPC + NVLink);
+            # "collective": NCCL all-to-all first.  Both must give the single-GPU result.
+            for mode in ("peer", "collective"):
+                for repeat in range(2):                      # the second call reuses cached IPC mappings
+                    k, v = sharded.sharded_sort_by_key(dev(keys[lo:hi]), dev(vals[lo:hi]), exchange=mode)
+                np.save(os.path.join(out_dir, f"{case}_k{rank}.npy"), k.cpu().numpy())
+                np.save(os.path.join(out_dir, f"{case}_v{rank}.npy"), v.cpu().numpy())
+                dist.barrier()
+                if rank == 0:
+                    kk = np.concatenate([np.load(os.path.join(out_dir, f"{case}_k{r}.npy")) for r in range(world)])
+                    vv = np.concatenate([np.load(os.path.join(out_dir, f"{case}_v{r}.npy")) for r in range(world)])
+                    wk, wv = o.sort_by_key(keys, vals)
+                    assert np.array_equal(kk, wk) and np.array_equal(vv, wv), (case, mode)
+                dist.barrier()
     finally:
         dist.destroy_process_group()
 

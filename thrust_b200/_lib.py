@@ -30,6 +30,9 @@ PROTOTYPES = {
     "tb200_merge_sort_by_key": [_vp, _vp, _vp, _vp, _sz, _i, _i, _i, _vp, _szp, _vp],
     "tb200_lower_bound": [_vp, _sz, _vp, _sz, _vp, _i, _i, _vp],
     "tb200_inclusive_scan_static": [_vp, _vp, _sz, _i, _i, _vp, _vp],
+    "tb200_ipc_export": [_vp, _vp, _szp],
+    "tb200_ipc_open": [_vp, _sz, C.POINTER(C.c_void_p)],
+    "tb200_ipc_close_all": [],
     "tb200_kernel_timing": [_i],
     "tb200_kernel_timing_read": [_i, C.POINTER(C.c_int), C.POINTER(C.c_float), C.POINTER(C.c_int)],
 }

@@ -63,6 +63,38 @@ class DeviceOps:
     def merge_by_key(self, ka, kb, va, vb, descending):
         return api.merge_by_key(ka, kb, va, vb, descending, sync=False)
 
+    supports_peer_reads = True
+
+    def export_buffer(self, t):
+        """64-byte IPC handle (as 8 int64) + byte offset of tensor t inside its allocation."""
+        import ctypes as C
+        lib = api._lib.load()
+        handle = np.zeros(8, dtype=np.int64)
+        off = C.c_size_t(0)
+        api._check(lib.tb200_ipc_export(api._ptr(t), C.c_void_p(handle.ctypes.data), C.byref(off)), "tb200_ipc_export")
+        return handle, int(off.value)
+
+    def open_buffer(self, handle, offset):
+        """Device pointer (int) in this process of a peer's exported buffer."""
+        import ctypes as C
+        lib = api._lib.load()
+        h = np.ascontiguousarray(handle, dtype=np.int64)
+        out = C.c_void_p(0)
+        api._check(lib.tb200_ipc_open(C.c_void_p(h.ctypes.data), int(offset), C.byref(out)), "tb200_ipc_open")
+        return int(out.value)
+
+    def merge_by_key_raw(self, ka, na, kb, nb, va, vb, key_dtype, val_dtype, descending, device):
+        """merge_by_key on raw device pointers (which may point into a peer GPU's memory)."""
+        import ctypes as C
+        lib = api._lib.load()
+        ko = torch.empty(na + nb, dtype=key_dtype, device=device)
+        vo = None if val_dtype is None else torch.empty(na + nb, dtype=val_dtype, device=device)
+        vbytes = 0 if vo is None else vo.element_size()
+        args = (C.c_void_p(ka), None if va is None else C.c_void_p(va), na, C.c_void_p(kb), None if vb is None else C.c_void_p(vb), nb,
+                api._ptr(ko), api._ptr(vo), api.DTYPE_CODE[key_dtype], vbytes, int(descending))
+        api._call_with_ws("merge", "tb200_merge_by_key", *args)
+        return ko, vo
+
     def lower_bound(self, sorted_keys, needles, descending):
         import ctypes as C
         lib = api._lib.load()
@@ -157,7 +189,7 @@ def choose_splitters(all_samples, world, descending=False):
 
 
 def sharded_sort_by_key(keys_local, vals_local=None, descending=False, group=None, ops=None, samples_per_rank=1024, stage_marks=None,
-                        consume_input=False):
+                        consume_input=False, exchange="auto"):
     """Stable sort of the concatenation of every rank's (keys_local, vals_local).  Returns this
     rank's slice (keys, vals) of the sorted sequence; slices are contiguous in rank order, sized by
     the splitters (about 1/G of the data each for sampled splitters).
@@ -166,6 +198,11 @@ def sharded_sort_by_key(keys_local, vals_local=None, descending=False, group=Non
     gather, all-gather of the samples, sort of the gathered sample and splitter pick, lower bounds,
     all-gather of the cut positions.  The host blocks once, to read the G x (G-1) cut positions that
     size the all-to-all; the merges after the exchange are enqueued without waiting again.
+    exchange: "collective" moves the pieces with an all-to-all (NCCL; pairwise send/recv on gloo) and
+    merges local copies; "peer" skips that copy: every rank publishes its sorted shard through CUDA
+    IPC and the first round of merges reads the pieces it needs directly out of the peers' memory
+    over NVLink with ordinary loads -- the exchange is fused into the merge kernel; "auto" picks
+    "peer" when the ops object supports it.
     consume_input=True sorts the local shard in place first (thrust::sort_by_key itself is an in-place
     algorithm) and so saves one copy of the shard; by default the inputs are left untouched.
     stage_marks, if a list, receives (label, callable) pairs where the callable records a marker on
@@ -192,9 +229,6 @@ def sharded_sort_by_key(keys_local, vals_local=None, descending=False, group=Non
     dist.all_gather_into_tensor(gathered, mine, group=group) if dist.get_backend(group) == "nccl" else \
         dist.all_gather(list(gathered.view(world, s).unbind(0)), mine, group=group)
     sizes_t = torch.tensor([n], dtype=torch.int64, device=dev)
-    all_sizes = torch.empty(world, dtype=torch.int64, device=dev)
-    dist.all_gather_into_tensor(all_sizes, sizes_t, group=group) if dist.get_backend(group) == "nccl" else \
-        dist.all_gather(list(all_sizes.view(world, 1).unbind(0)), sizes_t, group=group)
 
     # sort the gathered sample with the same kernels and take every (len/G)-th element as a splitter.
     # (ranks without data are rare; they are handled by the host path below)
@@ -203,15 +237,24 @@ def sharded_sort_by_key(keys_local, vals_local=None, descending=False, group=Non
     pos = torch.tensor([i * s for i in range(1, world)], dtype=torch.int64, device=dev)
     splitters = _plumbing_view(sample_keys)[pos].view(keys.dtype)
 
+    peer = exchange == "peer" or (exchange == "auto" and getattr(ops, "supports_peer_reads", False) and keys.is_cuda)
+    extra = np.zeros(0, np.int64)
+    if peer:
+        kh, koff = ops.export_buffer(keys)
+        vh, voff = (np.zeros(8, np.int64), 0) if vals is None else ops.export_buffer(vals)
+        extra = np.concatenate([kh, [koff], vh, [voff]]).astype(np.int64)
     cuts = ops.lower_bound(keys, splitters, descending)                       # [G-1] on the device
-    all_cuts = torch.empty(world * (world - 1), dtype=torch.int64, device=dev)
-    dist.all_gather_into_tensor(all_cuts, cuts, group=group) if dist.get_backend(group) == "nccl" else \
-        dist.all_gather(list(all_cuts.view(world, world - 1).unbind(0)), cuts, group=group)
+    row = torch.cat([cuts, sizes_t, torch.from_numpy(extra).to(dev)])
+    width = row.numel()
+    table = torch.empty(world * width, dtype=torch.int64, device=dev)
+    dist.all_gather_into_tensor(table, row, group=group) if dist.get_backend(group) == "nccl" else \
+        dist.all_gather(list(table.view(world, width).unbind(0)), row, group=group)
     mark("splitters")
-    # the one host wait: cut positions and shard sizes of every rank
-    meta = torch.cat([all_cuts, all_sizes]).cpu().numpy()
-    cut_matrix = meta[:world * (world - 1)].reshape(world, world - 1)
-    sizes_host = meta[world * (world - 1):]
+    # the one host wait: cut positions, shard sizes and buffer handles of every rank
+    meta = table.cpu().numpy().reshape(world, width)
+    cut_matrix = meta[:, :world - 1]
+    sizes_host = meta[:, world - 1]
+    handles = meta[:, world:]
     if (sizes_host == 0).any():
         # a rank without data contributed placeholder samples: redo the splitters on the host from the real ones
         real = np.concatenate([gathered.view(world, s)[r].cpu().numpy().view(_np_dtype(keys)) for r in range(world) if sizes_host[r] > 0]) \
@@ -220,6 +263,7 @@ def sharded_sort_by_key(keys_local, vals_local=None, descending=False, group=Non
             return keys, vals
         sp = choose_splitters(real, world, descending)
         cuts = ops.lower_bound(keys, torch.from_numpy(sp.copy()).to(dev), descending)
+        all_cuts = torch.empty(world * (world - 1), dtype=torch.int64, device=dev)
         dist.all_gather_into_tensor(all_cuts, cuts, group=group) if dist.get_backend(group) == "nccl" else \
             dist.all_gather(list(all_cuts.view(world, world - 1).unbind(0)), cuts, group=group)
         cut_matrix = all_cuts.cpu().numpy().reshape(world, world - 1)
@@ -229,6 +273,42 @@ def sharded_sort_by_key(keys_local, vals_local=None, descending=False, group=Non
     recv_counts = count_matrix[:, rank]
 
     mark("host_wait")
+    if peer:
+        # runs stay where they are: (pointer, length) pairs into the peers' published shards
+        ksz = keys.element_size()
+        vsz = 0 if vals is None else vals.element_size()
+        runs = []
+        for src in range(world):
+            start = int(bounds[src, rank])
+            cnt = int(count_matrix[src, rank])
+            if src == rank:
+                kp = keys.data_ptr()
+                vp = None if vals is None else vals.data_ptr()
+            else:
+                kp = ops.open_buffer(handles[src, 0:8], int(handles[src, 8]))
+                vp = None if vals is None else ops.open_buffer(handles[src, 9:17], int(handles[src, 17]))
+            runs.append((kp + start * ksz, None if vp is None else vp + start * vsz, cnt, None))
+        mark("exchange")
+        vdtype = None if vals is None else vals.dtype
+        while len(runs) > 1:
+            nxt = []
+            for i in range(0, len(runs) - 1, 2):
+                (ka, va, na, _), (kb, vb, nb, _) = runs[i], runs[i + 1]
+                ko, vo = ops.merge_by_key_raw(ka, na, kb, nb, va, vb, keys.dtype, vdtype, descending, dev)
+                nxt.append((ko.data_ptr(), None if vo is None else vo.data_ptr(), na + nb, (ko, vo)))   # keep the tensors alive
+            if len(runs) % 2:
+                nxt.append(runs[-1])
+            runs = nxt
+        kp, vp, cnt, owner = runs[0]
+        if owner is None:                                         # a lone run that was never merged is still a view of a shard: copy it
+            owner = ops.merge_by_key_raw(kp, cnt, kp, 0, vp, vp, keys.dtype, vdtype, descending, dev)
+        # nobody may reuse a shard while a peer still reads it: a collective on the stream orders
+        # every rank's merges before whatever the callers enqueue next
+        fence = torch.zeros(1, dtype=torch.int32, device=dev)
+        dist.all_reduce(fence, group=group)
+        mark("merge")
+        return owner
+
     rk = _exchange(keys, send_counts, recv_counts, group)
     rv = None if vals is None else _exchange(vals, send_counts, recv_counts, group)
     mark("exchange")
