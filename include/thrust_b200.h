@@ -178,6 +178,19 @@ int tb200_kernel_timing_read(int capacity, int* h_kernel_ids, float* h_ms, int* 
 int tb200_inclusive_scan_static(const void* d_in, void* d_out, size_t n, int t, int op,
                                 const void* h_init, tb200_stream_t stream);
 
+/* Stable merge of num_runs (<= 64) sorted runs, given as host arrays of device pointers and
+ * lengths, into d_keys_out / d_vals_out (sum of the lengths); ties keep the earlier run first.  A
+ * pairwise tree of merge-path merges ping-pongs between the output and the same-sized d_*_tmp
+ * buffers; everything is enqueued by this one call.  Run pointers may lie in a peer GPU's memory
+ * (tb200_ipc_open): this is the last stage of the multi-GPU sort, where the merges read the pieces
+ * they need straight out of the other GPUs' sorted shards.  Generalises
+ * thrust::merge_by_key (thrust/system/cuda/detail/merge.h:940-982) to many inputs; types as
+ * tb200_merge_by_key. */
+int tb200_merge_runs(const void* const* h_run_keys, const void* const* h_run_vals,
+                     const size_t* h_counts, int num_runs, void* d_keys_out, void* d_vals_out,
+                     void* d_keys_tmp, void* d_vals_tmp, int key_t, int val_bytes, int descending,
+                     void* d_ws, size_t* ws_bytes, tb200_stream_t stream);
+
 /* Sharing device buffers between the ranks of a one-process-per-GPU job, so that a kernel on one
  * GPU reads another GPU's buffer directly over NVLink with ordinary loads (the multi-GPU sort
  * merges the runs it needs straight out of its peers' memory instead of copying them first).

@@ -64,3 +64,30 @@ def test_full_size_merge_properties(tb):
     assert torch.equal(ki[from_a], a.view(torch.int64)) and torch.equal(ki[~from_a], b.view(torch.int64))
     ties = ki[1:] == ki[:-1]
     assert bool((~(from_a[1:] & ~from_a[:-1] & ties)).all())   # never B directly before an equal A
+
+
+@pytest.mark.parametrize("num_runs", [1, 2, 3, 5, 8])
+def test_merge_runs_tree(tb, port, num_runs):
+    """tb200_merge_runs: many sorted runs in one call, equal to folding the oracle's two-way merge
+    over them in order (ties keep the earlier run first)."""
+    import ctypes as C
+    from thrust_b200 import api
+    lib = tb._lib.load()
+    runs_k, runs_v, dk, dv = [], [], [], []
+    for r in range(num_runs):
+        n = [30011, 0, 4097, 1, 70001, 2816, 5, 12345][r]
+        k = np.sort((dg.rand64(80 + r, n) >> np.uint64(54)).astype(np.uint32))       # 10-bit keys: ties across runs
+        v = (np.arange(n, dtype=np.uint32) + np.uint32(r << 24))
+        runs_k.append(k); runs_v.append(v); dk.append(dev(k)); dv.append(dev(v))
+    total = sum(k.size for k in runs_k)
+    wk, wv = runs_k[0], runs_v[0]
+    for r in range(1, num_runs):
+        wk, wv = port.merge_by_key(wk, runs_k[r], wv, runs_v[r])
+    ko = torch.empty(total, dtype=torch.uint32, device="cuda"); kt = torch.empty_like(ko)
+    vo = torch.empty(total, dtype=torch.uint32, device="cuda"); vt = torch.empty_like(vo)
+    kp = (C.c_void_p * num_runs)(*[t.data_ptr() for t in dk])
+    vp = (C.c_void_p * num_runs)(*[t.data_ptr() for t in dv])
+    cn = (C.c_size_t * num_runs)(*[t.numel() for t in dk])
+    ws = api._call_with_ws("merge", "tb200_merge_runs", kp, vp, cn, num_runs, api._ptr(ko), api._ptr(vo), api._ptr(kt), api._ptr(vt), 5, 4, 0)
+    api._sync_and_check(ws, "merge_runs")
+    assert np.array_equal(host(ko), wk) and np.array_equal(host(vo), wv)

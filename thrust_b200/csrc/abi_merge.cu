@@ -37,3 +37,20 @@ TB200_API int tb200_merge_sort_by_key(void* d_keys, void* d_keys_alt, void* d_va
 #undef ARGS
   return ERR_UNSUPPORTED;
 }
+
+TB200_API int tb200_merge_runs(const void* const* h_run_keys, const void* const* h_run_vals, const size_t* h_counts, int num_runs, void* d_keys_out,
+                               void* d_vals_out, void* d_keys_tmp, void* d_vals_tmp, int key_t, int val_bytes, int descending, void* d_ws,
+                               size_t* ws_bytes, tb200_stream_t stream) {
+  if (!h_run_keys || !h_counts || (val_bytes && !h_run_vals)) return ERR_INVALID;
+#define ARGS h_run_keys, h_run_vals, h_counts, num_runs, d_keys_out, d_vals_out, d_keys_tmp, d_vals_tmp, val_bytes, descending, d_ws, ws_bytes, stream
+  switch (key_t) {
+    case TB200_I32: return merge_runs_for_key<int32_t>(ARGS);
+    case TB200_U32: return merge_runs_for_key<uint32_t>(ARGS);
+    case TB200_I64: return merge_runs_for_key<long long>(ARGS);
+    case TB200_U64: return merge_runs_for_key<unsigned long long>(ARGS);
+    case TB200_F32: return merge_runs_for_key<float>(ARGS);
+    case TB200_F64: return merge_runs_for_key<double>(ARGS);
+  }
+#undef ARGS
+  return ERR_UNSUPPORTED;
+}

@@ -95,6 +95,24 @@ class DeviceOps:
         api._call_with_ws("merge", "tb200_merge_by_key", *args)
         return ko, vo
 
+    def merge_runs_raw(self, runs, key_dtype, val_dtype, descending, device):
+        """Stable merge of many runs [(keys_ptr, vals_ptr or None, count)] with ONE library call."""
+        import ctypes as C
+        lib = api._lib.load()
+        m = len(runs)
+        total = sum(r[2] for r in runs)
+        ko = torch.empty(total, dtype=key_dtype, device=device)
+        kt = torch.empty(total, dtype=key_dtype, device=device)
+        vo = None if val_dtype is None else torch.empty(total, dtype=val_dtype, device=device)
+        vt = None if val_dtype is None else torch.empty(total, dtype=val_dtype, device=device)
+        kp = (C.c_void_p * m)(*[r[0] for r in runs])
+        vp = None if val_dtype is None else (C.c_void_p * m)(*[r[1] for r in runs])
+        cn = (C.c_size_t * m)(*[r[2] for r in runs])
+        vbytes = 0 if vo is None else vo.element_size()
+        api._call_with_ws("merge", "tb200_merge_runs", kp, vp, cn, m, api._ptr(ko), api._ptr(vo), api._ptr(kt), api._ptr(vt),
+                          api.DTYPE_CODE[key_dtype], vbytes, int(descending))
+        return ko, vo
+
     def lower_bound(self, sorted_keys, needles, descending):
         import ctypes as C
         lib = api._lib.load()
@@ -290,18 +308,21 @@ def sharded_sort_by_key(keys_local, vals_local=None, descending=False, group=Non
             runs.append((kp + start * ksz, None if vp is None else vp + start * vsz, cnt, None))
         mark("exchange")
         vdtype = None if vals is None else vals.dtype
-        while len(runs) > 1:
-            nxt = []
-            for i in range(0, len(runs) - 1, 2):
-                (ka, va, na, _), (kb, vb, nb, _) = runs[i], runs[i + 1]
-                ko, vo = ops.merge_by_key_raw(ka, na, kb, nb, va, vb, keys.dtype, vdtype, descending, dev)
-                nxt.append((ko.data_ptr(), None if vo is None else vo.data_ptr(), na + nb, (ko, vo)))   # keep the tensors alive
-            if len(runs) % 2:
-                nxt.append(runs[-1])
-            runs = nxt
-        kp, vp, cnt, owner = runs[0]
-        if owner is None:                                         # a lone run that was never merged is still a view of a shard: copy it
-            owner = ops.merge_by_key_raw(kp, cnt, kp, 0, vp, vp, keys.dtype, vdtype, descending, dev)
+        if hasattr(ops, "merge_runs_raw"):
+            owner = ops.merge_runs_raw([(r[0], r[1], r[2]) for r in runs], keys.dtype, vdtype, descending, dev)
+        else:
+            while len(runs) > 1:
+                nxt = []
+                for i in range(0, len(runs) - 1, 2):
+                    (ka, va, na, _), (kb, vb, nb, _) = runs[i], runs[i + 1]
+                    ko, vo = ops.merge_by_key_raw(ka, na, kb, nb, va, vb, keys.dtype, vdtype, descending, dev)
+                    nxt.append((ko.data_ptr(), None if vo is None else vo.data_ptr(), na + nb, (ko, vo)))   # keep the tensors alive
+                if len(runs) % 2:
+                    nxt.append(runs[-1])
+                runs = nxt
+            kp, vp, cnt, owner = runs[0]
+            if owner is None:                                     # a lone run that was never merged is still a view of a shard: copy it
+                owner = ops.merge_by_key_raw(kp, cnt, kp, 0, vp, vp, keys.dtype, vdtype, descending, dev)
         # nobody may reuse a shard while a peer still reads it: a collective on the stream orders
         # every rank's merges before whatever the callers enqueue next
         fence = torch.zeros(1, dtype=torch.int32, device=dev)
