@@ -191,6 +191,27 @@ int tb200_merge_runs(const void* const* h_run_keys, const void* const* h_run_val
                      void* d_keys_tmp, void* d_vals_tmp, int key_t, int val_bytes, int descending,
                      void* d_ws, size_t* ws_bytes, tb200_stream_t stream);
 
+/* The exchange step of the multi-GPU sort_by_key, fused with the collective: one kernel that
+ * splits a GPU's (key, value) pairs by key range and stores every pair straight into the receive
+ * buffer of the GPU that owns its range (ordinary stores over NVLink into buffers opened with
+ * tb200_ipc_open; a local pointer for the rank itself).  No counterpart in the reference.
+ *   d_splitters   num_buckets - 1 keys in ascending (descending=1: descending) order, on the device;
+ *                 bucket b holds the keys k with exactly b splitters <= k (in that order), so equal
+ *                 keys always share a bucket;
+ *   tb200_bucket_count   adds the bucket histogram of d_keys to d_counts[0, num_buckets) (zero it first);
+ *   tb200_bucket_scatter writes bucket b's pairs, in input order (stable), to
+ *                 h_dst_keys[b][h_dst_offsets[b] ...] and h_dst_vals[b][h_dst_offsets[b] ...].
+ * num_buckets <= 16, n < 2^30, key_t / val_bytes as tb200_sort_by_key.  The receivers must not touch
+ * their buffers until every sender's scatter has completed (order with a collective). */
+int tb200_bucket_count(const void* d_keys, size_t n, int key_t, int descending,
+                       const void* d_splitters, int num_buckets, unsigned long long* d_counts,
+                       tb200_stream_t stream);
+int tb200_bucket_scatter(const void* d_keys, const void* d_vals, size_t n, int key_t, int val_bytes,
+                         int descending, const void* d_splitters, int num_buckets,
+                         void* const* h_dst_keys, void* const* h_dst_vals,
+                         const unsigned long long* h_dst_offsets, void* d_ws, size_t* ws_bytes,
+                         tb200_stream_t stream);
+
 /* Sharing device buffers between the ranks of a one-process-per-GPU job, so that a kernel on one
  * GPU reads another GPU's buffer directly over NVLink with ordinary loads (the multi-GPU sort
  * merges the runs it needs straight out of its peers' memory instead of copying them first).

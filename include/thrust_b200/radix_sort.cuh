@@ -128,6 +128,7 @@ radix_hist_kernel(const UK* keys, size_t n, key_coding coding, int first_pass, i
 }
 
 // ---------------------------------------------------------------- 2. bucket bases + skip flags
+template <int UNUSED = 0>   // a template only so that the header can be included in several translation units
 __global__ void __launch_bounds__(RADIX_BINS)
 radix_scan_hist_kernel(radix_ctrl* ctrl, size_t n, int first_pass) {
   const int p = first_pass + blockIdx.x;
@@ -152,9 +153,45 @@ template <int KB, int VB> struct onesweep_tuning {
   static constexpr int IPT = KB <= 4 ? (VB == 0 ? 18 : VB <= 4 ? 16 : 12) : (VB == 0 ? 12 : VB <= 4 ? 10 : 8);
 };
 
-template <class UK, class UV, bool HAS_V, bool IS_FLOAT, class LB, int IPT, bool FULL>
-__device__ __forceinline__ void onesweep_tile(const UK* __restrict__ src, UK* __restrict__ dst, const UV* __restrict__ vsrc,
-                                              UV* __restrict__ vdst, unsigned n, unsigned tile, int shift, unsigned dmask,
+// What distinguishes a radix digit pass from the multi-GPU bucket scatter: how a key maps to one of
+// up to 256 bins and where a bin's items go.
+template <class UK, class UV, bool IS_FLOAT> struct radix_pass_policy {
+  static constexpr int BITS = RADIX_BITS;       // ballots per key
+  UK* dst; UV* vdst; int shift; unsigned dmask;
+  __device__ __forceinline__ unsigned digit(UK k) const { return key_digit<IS_FLOAT>(k, shift, dmask); }
+  __device__ __forceinline__ UK* keys_of(unsigned) const { return dst; }
+  __device__ __forceinline__ UV* vals_of(unsigned) const { return vdst; }
+};
+
+// Order-preserving unsigned code of a key (see the file header).
+template <class UK> __host__ __device__ __forceinline__ UK key_code(UK k, key_coding c) {
+  constexpr int B = 8 * sizeof(UK);
+  const UK sign = (UK)1 << (B - 1);
+  if (c.kind == KEY_SIGNED) k ^= sign;
+  else if (c.kind == KEY_FLOAT) k ^= (k & sign) ? (UK)~(UK)0 : sign;
+  return c.descending ? (UK)~k : k;
+}
+
+constexpr int MAX_BUCKETS = 16;
+// bin = number of splitters whose code is <= the key's code; bin b goes to destination b, which
+// may be a buffer in another GPU's memory (ordinary stores over NVLink)
+template <class UK, class UV> struct bucket_policy {
+  static constexpr int BITS = 4;
+  key_coding coding; int buckets;
+  const UK* split_code;      // shared memory: buckets - 1 codes, ascending
+  UK* const* dst_k; UV* const* dst_v;   // shared memory tables of destination pointers
+  __device__ __forceinline__ unsigned digit(UK k) const {
+    const UK c = key_code(k, coding);
+    unsigned d = 0;
+    for (int i = 0; i < buckets - 1; ++i) d += (c >= split_code[i]) ? 1u : 0u;
+    return d;
+  }
+  __device__ __forceinline__ UK* keys_of(unsigned d) const { return dst_k[d]; }
+  __device__ __forceinline__ UV* vals_of(unsigned d) const { return dst_v[d]; }
+};
+
+template <class UK, class UV, bool HAS_V, class Policy, class LB, int IPT, bool FULL>
+__device__ __forceinline__ void onesweep_tile(const UK* __restrict__ src, const UV* __restrict__ vsrc, unsigned n, unsigned tile, const Policy policy,
                                               const unsigned long long* bin_base, LB* lookback, unsigned* err,
                                               unsigned* warp_hist, unsigned* s_goff, unsigned* s_scan, UK* stage_k, UV* stage_v) {
   constexpr int NWARPS = ONESWEEP_BLOCK / 32;
@@ -162,6 +199,7 @@ __device__ __forceinline__ void onesweep_tile(const UK* __restrict__ src, UK* __
   constexpr int WCHUNK = 32 * IPT;
   constexpr int LB_BITS = 8 * sizeof(LB) - 2;
   constexpr LB LB_MASK = ((LB)1 << LB_BITS) - 1;
+  constexpr int PAD_DIGIT = (1 << Policy::BITS) - 1;
   const int lane = lane_id(), warp = threadIdx.x >> 5;
   const unsigned tile_base = tile * (unsigned)TILE;
   const unsigned tile_n = FULL ? (unsigned)TILE : n - tile_base;
@@ -180,13 +218,13 @@ __device__ __forceinline__ void onesweep_tile(const UK* __restrict__ src, UK* __
   const unsigned lanemask_lt = (1u << lane) - 1;
 #pragma unroll
   for (int i = 0; i < IPT; ++i) {
-    // a partial tile pads with pseudo-keys of digit 255: ranked after every real key of the tile
-    unsigned d = (FULL || wofs + i * 32 < tile_n) ? key_digit<IS_FLOAT>(key[i], shift, dmask) : (RADIX_BINS - 1);
+    // a partial tile pads with pseudo-keys of the highest digit: ranked after every real key of the tile
+    unsigned d = (FULL || wofs + i * 32 < tile_n) ? policy.digit(key[i]) : (unsigned)PAD_DIGIT;
     // lanes holding the same digit: one ballot per digit bit.  (match.any computes this in one
     // instruction but is issued at a small fraction of the ballot rate on sm_100.)
     unsigned peers = FULL_MASK;
 #pragma unroll
-    for (int b = 0; b < RADIX_BITS; ++b) {
+    for (int b = 0; b < Policy::BITS; ++b) {
       const bool bit = (d >> b) & 1;
       const unsigned vote = __ballot_sync(FULL_MASK, bit);
       peers &= bit ? vote : ~vote;
@@ -214,7 +252,7 @@ __device__ __forceinline__ void onesweep_tile(const UK* __restrict__ src, UK* __
   if (threadIdx.x < RADIX_BINS) {
     for (int w = 0; w < warp; ++w) digit_off += s_scan[w];
     unsigned real_count = my_count;
-    if (!FULL && threadIdx.x == RADIX_BINS - 1) real_count -= (unsigned)TILE - tile_n;
+    if (!FULL && threadIdx.x == PAD_DIGIT) real_count -= (unsigned)TILE - tile_n;
     LB* slot = lookback + (size_t)tile * RADIX_BINS + threadIdx.x;
     LB prefix = 0;
     if (tile == 0) {
@@ -263,7 +301,8 @@ __device__ __forceinline__ void onesweep_tile(const UK* __restrict__ src, UK* __
     unsigned j = threadIdx.x + i * ONESWEEP_BLOCK;
     if (FULL || j < tile_n) {
       UK k = stage_k[j];
-      dst[s_goff[key_digit<IS_FLOAT>(k, shift, dmask)] + j] = k;
+      const unsigned d = policy.digit(k);
+      policy.keys_of(d)[s_goff[d] + j] = k;
     }
   }
   if constexpr (HAS_V) {
@@ -273,7 +312,10 @@ __device__ __forceinline__ void onesweep_tile(const UK* __restrict__ src, UK* __
 #pragma unroll
     for (int i = 0; i < IPT; ++i) {
       unsigned j = threadIdx.x + i * ONESWEEP_BLOCK;
-      if (FULL || j < tile_n) vdst[s_goff[key_digit<IS_FLOAT>(stage_k[j], shift, dmask)] + j] = stage_v[j];
+      if (FULL || j < tile_n) {
+        const unsigned d = policy.digit(stage_k[j]);
+        policy.vals_of(d)[s_goff[d] + j] = stage_v[j];
+      }
     }
   }
 }
@@ -307,12 +349,87 @@ onesweep_kernel(UK* buf_a, UK* buf_b, UV* val_a, UV* val_b, unsigned n, key_codi
   const int shift = pass * RADIX_BITS;
   const unsigned dmask = digit_mask<UK>(coding, shift);
   const bool full = (unsigned long long)(tile + 1) * TILE <= n;
+  using Policy = radix_pass_policy<UK, UV, IS_FLOAT>;
+  const Policy policy{dst, vdst, shift, dmask};
   if (full)
-    onesweep_tile<UK, UV, HAS_V, IS_FLOAT, LB, IPT, true>(src, dst, vsrc, vdst, n, tile, shift, dmask, ctrl->hist[pass], lookback, &hdr->error,
-                                                          warp_hist, s_goff, s_scan, stage_k, stage_v);
+    onesweep_tile<UK, UV, HAS_V, Policy, LB, IPT, true>(src, vsrc, n, tile, policy, ctrl->hist[pass], lookback, &hdr->error, warp_hist, s_goff, s_scan,
+                                                        stage_k, stage_v);
   else
-    onesweep_tile<UK, UV, HAS_V, IS_FLOAT, LB, IPT, false>(src, dst, vsrc, vdst, n, tile, shift, dmask, ctrl->hist[pass], lookback, &hdr->error,
-                                                           warp_hist, s_goff, s_scan, stage_k, stage_v);
+    onesweep_tile<UK, UV, HAS_V, Policy, LB, IPT, false>(src, vsrc, n, tile, policy, ctrl->hist[pass], lookback, &hdr->error, warp_hist, s_goff, s_scan,
+                                                         stage_k, stage_v);
+}
+
+// ---------------------------------------------------------------- multi-GPU: bucket count and scatter
+// Destination table handed to the scatter kernel by value.
+template <class UK, class UV> struct bucket_table {
+  UK* dst_k[MAX_BUCKETS]; UV* dst_v[MAX_BUCKETS]; unsigned long long base[MAX_BUCKETS];
+};
+
+// counts[b] = number of keys whose code falls into bucket b (b = number of splitters <= code).
+// Lane-private copies of the 16 bins in shared memory keep the atomics conflict-free.
+template <class UK>
+__global__ void __launch_bounds__(256)
+bucket_count_kernel(const UK* keys, size_t n, key_coding coding, const UK* splitters, int buckets, unsigned long long* counts) {
+  __shared__ UK code[MAX_BUCKETS];
+  __shared__ unsigned local[MAX_BUCKETS * 32];
+  for (int i = threadIdx.x; i < MAX_BUCKETS * 32; i += 256) local[i] = 0;
+  if ((int)threadIdx.x < buckets - 1) code[threadIdx.x] = key_code(splitters[threadIdx.x], coding);
+  __syncthreads();
+  const int lane = lane_id();
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const UK c = key_code(__ldcs(keys + i), coding);
+    unsigned d = 0;
+    for (int s = 0; s < buckets - 1; ++s) d += (c >= code[s]) ? 1u : 0u;
+    atomicAdd(&local[d * 32 + lane], 1u);
+  }
+  __syncthreads();
+  if ((int)threadIdx.x < buckets) {
+    unsigned total = 0;
+    for (int q = 0; q < 32; ++q) total += local[threadIdx.x * 32 + ((q + threadIdx.x) & 31)];
+    if (total) atomicAdd(&counts[threadIdx.x], (unsigned long long)total);
+  }
+}
+
+// Stable scatter of (key, value) pairs into per-bucket destinations: item order inside a bucket
+// is input order, bucket b's items land at dst[b][base[b] ...].  Same tile machinery as a radix
+// pass (ballot ranking, per-bin look-back, staging so that each bin's run is stored contiguously);
+// only the bin function and the destinations differ.
+template <class UK, class UV, bool HAS_V, class LB, int IPT>
+__global__ void __launch_bounds__(ONESWEEP_BLOCK, 2)
+bucket_scatter_kernel(const UK* src, const UV* vsrc, unsigned n, key_coding coding, const UK* splitters, int buckets, bucket_table<UK, UV> table,
+                      LB* lookback, ws_header* hdr) {
+  constexpr int NWARPS = ONESWEEP_BLOCK / 32;
+  constexpr int TILE = ONESWEEP_BLOCK * IPT;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  unsigned* warp_hist = reinterpret_cast<unsigned*>(smem_raw);
+  unsigned* s_goff = warp_hist + NWARPS * RADIX_BINS;
+  unsigned* s_scan = s_goff + RADIX_BINS;
+  UK* stage_k = reinterpret_cast<UK*>(s_scan + 16);
+  UV* stage_v = reinterpret_cast<UV*>(stage_k + TILE);
+  __shared__ unsigned s_tile;
+  __shared__ UK s_code[MAX_BUCKETS];
+  __shared__ UK* s_dst_k[MAX_BUCKETS];
+  __shared__ UV* s_dst_v[MAX_BUCKETS];
+  __shared__ unsigned long long s_base[RADIX_BINS];
+
+  if (threadIdx.x == 0) s_tile = atomicAdd(&hdr->ticket, 1u);
+  for (int i = threadIdx.x; i < NWARPS * RADIX_BINS; i += ONESWEEP_BLOCK) warp_hist[i] = 0;
+  if (threadIdx.x < RADIX_BINS) s_base[threadIdx.x] = threadIdx.x < MAX_BUCKETS ? table.base[threadIdx.x] : 0ull;
+  if (threadIdx.x < MAX_BUCKETS) {
+    s_dst_k[threadIdx.x] = table.dst_k[threadIdx.x];
+    s_dst_v[threadIdx.x] = table.dst_v[threadIdx.x];
+    if ((int)threadIdx.x < buckets - 1) s_code[threadIdx.x] = key_code(splitters[threadIdx.x], coding);
+  }
+  __syncthreads();
+  const unsigned tile = s_tile;
+  using Policy = bucket_policy<UK, UV>;
+  const Policy policy{coding, buckets, s_code, s_dst_k, s_dst_v};
+  const bool full = (unsigned long long)(tile + 1) * TILE <= n;
+  if (full)
+    onesweep_tile<UK, UV, HAS_V, Policy, LB, IPT, true>(src, vsrc, n, tile, policy, s_base, lookback, &hdr->error, warp_hist, s_goff, s_scan, stage_k, stage_v);
+  else
+    onesweep_tile<UK, UV, HAS_V, Policy, LB, IPT, false>(src, vsrc, n, tile, policy, s_base, lookback, &hdr->error, warp_hist, s_goff, s_scan, stage_k, stage_v);
 }
 
 // ---------------------------------------------------------------- 4. copy back after an odd number of passes
@@ -374,7 +491,7 @@ cudaError_t radix_sort_async(UK* keys_a, UK* keys_b, UV* vals_a, UV* vals_b, siz
   if ((e = cudaFuncSetAttribute(hk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hist_smem)) != cudaSuccess) return e;
   { timed_launch tl(KID_RADIX_HIST, stream);
   hk<<<(unsigned)hist_grid, HIST_BLOCK, hist_smem, stream>>>(keys_a, n, coding, first_pass, num_passes, ctrl); }
-  radix_scan_hist_kernel<<<num_passes, RADIX_BINS, 0, stream>>>(ctrl, n, first_pass);
+  radix_scan_hist_kernel<><<<num_passes, RADIX_BINS, 0, stream>>>(ctrl, n, first_pass);
 
   const size_t smem = onesweep_smem_bytes<KB, VB>();
   const bool isf = coding.kind == KEY_FLOAT;
@@ -395,6 +512,44 @@ cudaError_t radix_sort_async(UK* keys_a, UK* keys_b, UV* vals_a, UV* vals_b, siz
   size_t cb_grid = (n + 256 * 8 - 1) / (256 * 8);
   if (cb_grid > (size_t)di.sm_count * 8) cb_grid = (size_t)di.sm_count * 8;
   radix_copy_back_kernel<UK, UV, HAS_V><<<(unsigned)cb_grid, 256, 0, stream>>>(keys_a, keys_b, vals_a, vals_b, n, first_pass, num_passes, ctrl);
+  return cudaGetLastError();
+}
+
+// counts[0..buckets) += histogram of bucket ids (the caller zeroes counts); no sync
+template <class UK>
+cudaError_t bucket_count_async(const UK* keys, size_t n, key_coding coding, const UK* d_splitters, int buckets, unsigned long long* d_counts,
+                               cudaStream_t stream) {
+  if (buckets < 1 || buckets > MAX_BUCKETS) return cudaErrorInvalidValue;
+  if (n == 0) return cudaSuccess;
+  const device_info& di = current_device_info();
+  size_t grid = (n + 256 * 16 - 1) / (256 * 16);
+  if (grid > (size_t)di.sm_count * 8) grid = (size_t)di.sm_count * 8;
+  bucket_count_kernel<UK><<<(unsigned)grid, 256, 0, stream>>>(keys, n, coding, d_splitters, buckets, d_counts);
+  return cudaGetLastError();
+}
+
+template <int KB, int VB> size_t bucket_scatter_workspace_bytes(size_t n) {
+  size_t tiles = (n + onesweep_tile_items<KB, VB>() - 1) / onesweep_tile_items<KB, VB>();
+  return sizeof(ws_header) + align_up(tiles * RADIX_BINS * 4, 256);
+}
+
+// Stable scatter into up to MAX_BUCKETS destinations (see bucket_scatter_kernel); n < 2^30.  No sync.
+template <class UK, class UV, bool HAS_V>
+cudaError_t bucket_scatter_async(const UK* keys, const UV* vals, size_t n, key_coding coding, const UK* d_splitters, int buckets,
+                                 const bucket_table<UK, UV>& table, void* ws, cudaStream_t stream) {
+  constexpr int KB = sizeof(UK);
+  constexpr int VB = HAS_V ? sizeof(UV) : 0;
+  constexpr int IPT = onesweep_tuning<KB, VB>::IPT;
+  if (buckets < 1 || buckets > MAX_BUCKETS || n >= (1ull << 30)) return cudaErrorInvalidValue;
+  cudaError_t e = cudaMemsetAsync(ws, 0, bucket_scatter_workspace_bytes<KB, VB>(n), stream);
+  if (e != cudaSuccess || n == 0) return e;
+  const size_t tiles = (n + onesweep_tile_items<KB, VB>() - 1) / onesweep_tile_items<KB, VB>();
+  char* base = static_cast<char*>(ws);
+  auto kern = bucket_scatter_kernel<UK, UV, HAS_V, uint32_t, IPT>;
+  const size_t smem = onesweep_smem_bytes<KB, VB>();
+  if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
+  kern<<<(unsigned)tiles, ONESWEEP_BLOCK, smem, stream>>>(keys, vals, (unsigned)n, coding, d_splitters, buckets, table,
+                                                        reinterpret_cast<uint32_t*>(base + sizeof(ws_header)), reinterpret_cast<ws_header*>(base));
   return cudaGetLastError();
 }
 

@@ -34,9 +34,10 @@ def _worker(rank, world, port, out_dir):
         for case, keys in (("uniform", dg.sort_keys_u32(n_total)), ("ties", (dg.sort_keys_u32(n_total) >> np.uint32(22)).astype(np.uint32)),
                            ("u64", dg.sort_keys_u64_40bit(n_total))):
             vals = np.arange(n_total, dtype=np.uint32)
+            # "scatter": one kernel per GPU stores every pair into its owner's receive buffer, then a local sort;
             # "peer": merges read the pieces straight out of the other GPUs' memory (CUDA IPC + NVLink);
             # "collective": NCCL all-to-all first.  Both must give the single-GPU result.
-            for mode in ("peer", "collective"):
+            for mode in ("scatter", "peer", "collective"):
                 for repeat in range(2):                      # the second call reuses cached IPC mappings
                     k, v = sharded.sharded_sort_by_key(dev(keys[lo:hi]), dev(vals[lo:hi]), exchange=mode)
                 np.save(os.path.join(out_dir, f"{case}_k{rank}.npy"), k.cpu().numpy())

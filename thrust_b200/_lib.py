@@ -29,6 +29,8 @@ PROTOTYPES = {
     "tb200_merge_by_key": [_vp, _vp, _sz, _vp, _vp, _sz, _vp, _vp, _i, _i, _i, _vp, _szp, _vp],
     "tb200_merge_sort_by_key": [_vp, _vp, _vp, _vp, _sz, _i, _i, _i, _vp, _szp, _vp],
     "tb200_merge_runs": [_vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _szp, _vp],
+    "tb200_bucket_count": [_vp, _sz, _i, _i, _vp, _i, _vp, _vp],
+    "tb200_bucket_scatter": [_vp, _vp, _sz, _i, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _szp, _vp],
     "tb200_lower_bound": [_vp, _sz, _vp, _sz, _vp, _i, _i, _vp],
     "tb200_inclusive_scan_static": [_vp, _vp, _sz, _i, _i, _vp, _vp],
     "tb200_ipc_export": [_vp, _vp, _szp],

@@ -95,6 +95,37 @@ class DeviceOps:
         api._call_with_ws("merge", "tb200_merge_by_key", *args)
         return ko, vo
 
+    def bucket_count(self, keys, splitters, buckets, descending):
+        import ctypes as C
+        lib = api._lib.load()
+        counts = torch.zeros(buckets, dtype=torch.int64, device=keys.device)
+        api._check(lib.tb200_bucket_count(api._ptr(keys), keys.numel(), api.DTYPE_CODE[keys.dtype], int(descending), api._ptr(splitters), buckets,
+                                          api._ptr(counts), api._stream()), "tb200_bucket_count")
+        return counts
+
+    def bucket_scatter(self, keys, vals, splitters, dst_keys, dst_vals, dst_offsets, descending):
+        """Stable scatter of this rank's pairs into the receive buffers (device pointers, possibly on peers)."""
+        import ctypes as C
+        m = len(dst_keys)
+        kp = (C.c_void_p * m)(*dst_keys)
+        vp = None if vals is None else (C.c_void_p * m)(*dst_vals)
+        off = (C.c_ulonglong * m)(*[int(o) for o in dst_offsets])
+        api._call_with_ws("scatter", "tb200_bucket_scatter", api._ptr(keys), api._ptr(vals), keys.numel(), api.DTYPE_CODE[keys.dtype],
+                          0 if vals is None else vals.element_size(), int(descending), api._ptr(splitters), m, kp, vp, off)
+
+    _recv_cache = {}
+
+    def receive_buffers(self, device, key_dtype, val_dtype, capacity):
+        """Receive buffers of the scatter exchange, kept across calls so that their IPC handles stay valid."""
+        key = (str(device), key_dtype, val_dtype)
+        have = self._recv_cache.get(key)
+        if have is None or have[0].numel() < capacity:
+            k = torch.empty(capacity, dtype=key_dtype, device=device)
+            v = None if val_dtype is None else torch.empty(capacity, dtype=val_dtype, device=device)
+            have = (k, v, self.export_buffer(k), None if v is None else self.export_buffer(v))
+            self._recv_cache[key] = have
+        return have
+
     def merge_runs_raw(self, runs, key_dtype, val_dtype, descending, device):
         """Stable merge of many runs [(keys_ptr, vals_ptr or None, count)] with ONE library call."""
         import ctypes as C
@@ -206,6 +237,85 @@ def choose_splitters(all_samples, world, descending=False):
     return np.ascontiguousarray(s[pos])
 
 
+def _gather_rows(row, world, group):
+    """all-gather of one int64 row per rank; returns the [world, width] table on the host (the host wait)."""
+    width = row.numel()
+    table = torch.empty(world * width, dtype=torch.int64, device=row.device)
+    if dist.get_backend(group) == "nccl":
+        dist.all_gather_into_tensor(table, row, group=group)
+    else:
+        dist.all_gather(list(table.view(world, width).unbind(0)), row, group=group)
+    return table.cpu().numpy().reshape(world, width)
+
+
+def _device_splitters(keys, n, world, descending, group, ops, samples_per_rank):
+    """G-1 splitters on the device: regular samples of every shard, all-gathered, sorted with the
+    library's own sort, every (len/G)-th element taken.  No host wait."""
+    dev = keys.device
+    s = samples_per_rank
+    pick = torch.from_numpy(((np.arange(s, dtype=np.int64) * 2 + 1) * max(n, 1) // (2 * s))).to(dev)
+    kview = _plumbing_view(keys)
+    mine = kview[pick] if n else torch.zeros(s, dtype=kview.dtype, device=dev)
+    gathered = torch.empty(world * s, dtype=kview.dtype, device=dev)
+    if dist.get_backend(group) == "nccl":
+        dist.all_gather_into_tensor(gathered, mine, group=group)
+    else:
+        dist.all_gather(list(gathered.view(world, s).unbind(0)), mine, group=group)
+    sample_keys = gathered.view(keys.dtype)
+    ops.sort_by_key(sample_keys, None, descending)
+    pos = torch.tensor([i * s for i in range(1, world)], dtype=torch.int64, device=dev)
+    return _plumbing_view(sample_keys)[pos].view(keys.dtype), gathered
+
+
+def _sort_by_scatter(keys, vals, descending, group, ops, samples_per_rank, mark):
+    """The scatter route of sharded_sort_by_key; returns None if some receive buffer is too small
+    (every rank takes the same decision from the same table)."""
+    world, rank = _world(group)
+    dev = keys.device
+    n = keys.numel()
+    if n == 0 or n >= (1 << 30):
+        flag = torch.tensor([1], dtype=torch.int64, device=dev)
+    else:
+        flag = torch.tensor([0], dtype=torch.int64, device=dev)
+    splitters, _ = _device_splitters(keys, n, world, descending, group, ops, samples_per_rank)
+    counts = ops.bucket_count(keys, splitters, world, descending)
+    capacity = int(1.5 * n) + 65536
+    rk, rv, kexp, vexp = ops.receive_buffers(dev, keys.dtype, None if vals is None else vals.dtype, capacity)
+    extra = np.concatenate([[rk.numel()], kexp[0], [kexp[1]], (vexp[0] if vexp else np.zeros(8, np.int64)), [vexp[1] if vexp else 0]]).astype(np.int64)
+    row = torch.cat([counts, flag, torch.from_numpy(extra).to(dev)])
+    mark("splitters")
+    meta = _gather_rows(row, world, group)                                     # the one host wait
+    mark("host_wait")
+    count_matrix = meta[:, :world]                                             # [src][dst]
+    unusable = meta[:, world].any()
+    caps = meta[:, world + 1]
+    handles = meta[:, world + 2:]
+    recv_total = count_matrix.sum(axis=0)
+    if unusable or (recv_total > caps).any():
+        return None
+    offsets = np.cumsum(count_matrix, axis=0) - count_matrix                   # rows before mine, per destination
+    dst_k, dst_v = [], []
+    for d in range(world):
+        if d == rank:
+            dst_k.append(rk.data_ptr())
+            dst_v.append(None if rv is None else rv.data_ptr())
+        else:
+            dst_k.append(ops.open_buffer(handles[d, 0:8], int(handles[d, 8])))
+            dst_v.append(None if rv is None else ops.open_buffer(handles[d, 9:17], int(handles[d, 17])))
+    ops.bucket_scatter(keys, vals, splitters, dst_k, dst_v, offsets[rank], descending)
+    # every sender's stores must have landed before a receiver sorts its buffer
+    fence = torch.zeros(1, dtype=torch.int32, device=dev)
+    dist.all_reduce(fence, group=group)
+    mark("exchange")
+    m = int(recv_total[rank])
+    out_k = rk[:m]
+    out_v = None if rv is None else rv[:m]
+    ops.sort_by_key(out_k, out_v, descending)
+    res = (out_k.clone(), None if out_v is None else out_v.clone())          # the receive buffers are reused by the next call
+    mark("local_sort")
+    return res
+
+
 def sharded_sort_by_key(keys_local, vals_local=None, descending=False, group=None, ops=None, samples_per_rank=1024, stage_marks=None,
                         consume_input=False, exchange="auto"):
     """Stable sort of the concatenation of every rank's (keys_local, vals_local).  Returns this
@@ -216,7 +326,11 @@ def sharded_sort_by_key(keys_local, vals_local=None, descending=False, group=Non
     gather, all-gather of the samples, sort of the gathered sample and splitter pick, lower bounds,
     all-gather of the cut positions.  The host blocks once, to read the G x (G-1) cut positions that
     size the all-to-all; the merges after the exchange are enqueued without waiting again.
-    exchange: "collective" moves the pieces with an all-to-all (NCCL; pairwise send/recv on gloo) and
+    exchange: "scatter" (the default where available) does not sort first: it samples splitters from
+    the unsorted shard, counts and exchanges bucket sizes, and then ONE kernel per GPU splits its
+    pairs by key range and stores each pair straight into the owning GPU's receive buffer over
+    NVLink (stable: source-rank-major, input order inside a source); a stable local radix sort of
+    what was received finishes the job.  "collective" moves the pieces with an all-to-all (NCCL; pairwise send/recv on gloo) and
     merges local copies; "peer" skips that copy: every rank publishes its sorted shard through CUDA
     IPC and the first round of merges reads the pieces it needs directly out of the peers' memory
     over NVLink with ordinary loads -- the exchange is fused into the merge kernel; "auto" picks
@@ -228,6 +342,12 @@ def sharded_sort_by_key(keys_local, vals_local=None, descending=False, group=Non
     ops = ops or DeviceOps()
     mark = (lambda label: stage_marks.append((label, stage_marks[0][1]()))) if stage_marks else (lambda label: None)
     world, rank = _world(group)
+    can_peer = getattr(ops, "supports_peer_reads", False) and keys_local.is_cuda
+    if world > 1 and (exchange == "scatter" or (exchange == "auto" and can_peer and world <= 16)):
+        done = _sort_by_scatter(keys_local, vals_local, descending, group, ops, samples_per_rank, mark)
+        if done is not None:
+            return done
+        exchange = "peer"                       # a receive buffer would have overflowed: take the merge route
     dev = keys_local.device
     n = keys_local.numel()
     keys = keys_local if consume_input else keys_local.clone()
@@ -255,7 +375,7 @@ def sharded_sort_by_key(keys_local, vals_local=None, descending=False, group=Non
     pos = torch.tensor([i * s for i in range(1, world)], dtype=torch.int64, device=dev)
     splitters = _plumbing_view(sample_keys)[pos].view(keys.dtype)
 
-    peer = exchange == "peer" or (exchange == "auto" and getattr(ops, "supports_peer_reads", False) and keys.is_cuda)
+    peer = exchange == "peer" or (exchange == "auto" and can_peer)
     extra = np.zeros(0, np.int64)
     if peer:
         kh, koff = ops.export_buffer(keys)
