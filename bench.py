@@ -17,8 +17,8 @@ value = original index).  Rank 0 prints ONE JSON line:
   others       the remaining hot-path algorithms at their benchmark sizes (N=1 only).
 
 With N > 1 (torchrun, one rank per GPU) the same 2^28 pairs are split across the ranks and sorted
-by thrust_b200.sharded.sharded_sort_by_key: per-GPU radix sort, sampled splitters, then per-GPU
-merges that read the pieces they need directly from the peers' memory over NVLink ("scaling": "strong").  `--impl reference` times the
+by thrust_b200.sharded.sharded_sort_by_key: sampled splitters, one scatter kernel per GPU that stores
+each pair into its owner's receive buffer over NVLink (CUDA IPC), then a stable per-GPU radix sort ("scaling": "strong").  `--impl reference` times the
 reference's own CPU implementation (OpenMP backend) on the host cores instead.
 """
 import argparse
@@ -320,8 +320,8 @@ def run_ours(args):
         def step():
             # like thrust::sort_by_key, the sharded sort may consume its input
             out["k"], out["v"] = sharded.sharded_sort_by_key(k, v, consume_input=True)
-        # per rank: local sort (7) + sample sort (7) + lower_bound (1) + G-1 merges of (partition + merge) kernels
-        launches_per_step = 7 + 7 + 1 + 2 * (world - 1)
+        # per rank: sample sort (7) + bucket count (1) + bucket scatter (1) + local sort (7)
+        launches_per_step = 7 + 1 + 1 + 7
 
     # the clock sampler runs from before the warm-up to after the timed steps, so that even a timed
     # region of a few tens of milliseconds is covered by samples taken under the same load
