@@ -162,8 +162,20 @@ def read_kernel_times(lib, kernel_id):
 
 
 def bench_others(torch, tb, lib, peak):
-    """The other hot-path algorithms at their benchmark sizes; median of 10 C-ABI calls each."""
+    """The other hot-path algorithms at their benchmark sizes; median of 10 C-ABI calls each.  Each
+    line also carries the reference Thrust's OpenMP backend on the host cores (oracle/_ref), timed
+    once after a warm-up on a bounded sample of the same workload."""
     from thrust_b200 import datagen as dg
+    from oracle import oracle
+    ora = oracle.load_best()
+    cpu_n = 1 << 25
+
+    def cpu_time(fn, units):
+        fn()
+        t0 = time.perf_counter()
+        fn()
+        dt = time.perf_counter() - t0
+        return {"value": units / dt / 1e9, "cores": ora.threads, "kind": ora.kind, "sample_units": units, "seconds": dt}
     st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
     p = lambda t: None if t is None else C.c_void_p(t.data_ptr())  # noqa: E731
     dev = lambda a: torch.from_numpy(a).cuda()  # noqa: E731
@@ -174,7 +186,7 @@ def bench_others(torch, tb, lib, peak):
         assert getattr(lib, fn)(*a, None, C.byref(need), None) == 0
         return torch.empty(max(need.value, 256), dtype=torch.uint8, device="cuda"), need
 
-    def record(name, n_units, bytes_per_unit, fn, setup=None, reps=10, unit="Gelem/s"):
+    def record(name, n_units, bytes_per_unit, fn, setup=None, reps=10, unit="Gelem/s", cpu=None):
         for _ in range(3):
             if setup:
                 setup()
@@ -183,20 +195,25 @@ def bench_others(torch, tb, lib, peak):
         ms = float(np.median(ts))
         gbs = n_units * bytes_per_unit / ms / 1e6
         res.append({"name": name, "value": n_units / ms / 1e6, "unit": unit, "ms": ms, "algorithmic_bytes_per_unit": bytes_per_unit,
-                    "achieved_gbs": gbs, "frac_of_hbm_peak": gbs / peak})
+                    "achieved_gbs": gbs, "frac_of_hbm_peak": gbs / peak, "cpu_reference": cpu})
 
     n = 1 << 28
     x = dev(dg.reduce_input(n))
     out8 = torch.empty(1, dtype=torch.int64, device="cuda")
     init = np.zeros((), np.int64)
     ws, need = ws_for("tb200_reduce", None, n, 4, 6, 0, None, None)
+    hx = dg.reduce_input(cpu_n)
     record("reduce int32->int64 2^28", n, 4,
-           lambda: lib.tb200_reduce(p(x), n, 4, 6, 0, C.c_void_p(init.ctypes.data), p(out8), p(ws), C.byref(need), st))
+           lambda: lib.tb200_reduce(p(x), n, 4, 6, 0, C.c_void_p(init.ctypes.data), p(out8), p(ws), C.byref(need), st),
+           cpu=cpu_time(lambda: ora.reduce(hx, np.int64(0)), cpu_n))
     del x
     s = dev(dg.scan_input_i32(n))
     o = torch.empty_like(s)
     ws, need = ws_for("tb200_inclusive_scan", None, None, n, 4, 0, None)
-    record("inclusive_scan int32 2^28", n, 8, lambda: lib.tb200_inclusive_scan(p(s), p(o), n, 4, 0, None, p(ws), C.byref(need), st))
+    hs = dg.scan_input_i32(cpu_n)
+    hso = np.empty_like(hs)
+    record("inclusive_scan int32 2^28", n, 8, lambda: lib.tb200_inclusive_scan(p(s), p(o), n, 4, 0, None, p(ws), C.byref(need), st),
+           cpu=cpu_time(lambda: ora.inclusive_scan(hs, out=hso), cpu_n))
     zero = np.zeros((), np.int32)
     record("exclusive_scan int32 2^28", n, 8,
            lambda: lib.tb200_exclusive_scan(p(s), p(o), n, 4, 0, C.c_void_p(zero.ctypes.data), p(ws), C.byref(need), st))
@@ -208,21 +225,30 @@ def bench_others(torch, tb, lib, peak):
     o1, o2 = torch.empty_like(c), torch.empty_like(c)
     cnt = torch.zeros(1, dtype=torch.int64, device="cuda")
     ws, need = ws_for("tb200_partition", None, n, 4, 0, 2, 0, None)
-    record("copy_if x%2==0 int32 2^28", n, 6, lambda: lib.tb200_copy_if(p(c), None, p(o1), n, 4, 0, 0, 2, 0, p(cnt), p(ws), C.byref(need), st))
+    hc = dg.compaction_input(cpu_n)
+    record("copy_if x%2==0 int32 2^28", n, 6, lambda: lib.tb200_copy_if(p(c), None, p(o1), n, 4, 0, 0, 2, 0, p(cnt), p(ws), C.byref(need), st),
+           cpu=cpu_time(lambda: ora.copy_if(hc, "mod_eq", 2, 0), cpu_n))
     record("partition_copy x%2==0 int32 2^28", n, 8,
            lambda: lib.tb200_partition_copy(p(c), None, p(o1), p(o2), n, 4, 0, 0, 2, 0, p(cnt), p(ws), C.byref(need), st))
     record("partition (in place) x%2==0 int32 2^28", n, 8, lambda: lib.tb200_partition(p(o1), n, 4, 0, 2, 0, p(cnt), p(ws), C.byref(need), st),
-           setup=lambda: o1.copy_(c))
+           setup=lambda: o1.copy_(c), cpu=cpu_time(lambda: ora.stable_partition(hc, "mod_eq", 2, 0), cpu_n))
     del c
     keys = dev(dg.run_keys(n))
-    record("unique_copy int32 runs(mean 4) 2^28", n, 5, lambda: lib.tb200_unique_copy(p(keys), p(o1), n, 4, p(cnt), p(ws), C.byref(need), st))
+    hk = dg.run_keys(cpu_n)
+    hv = dg.run_values_f32(cpu_n)
+    record("unique_copy int32 runs(mean 4) 2^28", n, 5, lambda: lib.tb200_unique_copy(p(keys), p(o1), n, 4, p(cnt), p(ws), C.byref(need), st),
+           cpu=cpu_time(lambda: ora.unique_copy(hk), cpu_n))
     vals = dev(dg.run_values_f32(n))
     vo = o2.view(torch.float32)
     ws2, need2 = ws_for("tb200_reduce_by_key", None, None, None, None, n, 4, 8, 0, None)
     record("reduce_by_key int32/fp32 runs(mean 4) 2^28", n, 10,
-           lambda: lib.tb200_reduce_by_key(p(keys), p(vals), p(o1), p(vo), n, 4, 8, 0, p(cnt), p(ws2), C.byref(need2), st))
+           lambda: lib.tb200_reduce_by_key(p(keys), p(vals), p(o1), p(vo), n, 4, 8, 0, p(cnt), p(ws2), C.byref(need2), st),
+           cpu=cpu_time(lambda: ora.reduce_by_key(hk, hv), cpu_n))
     del keys, vals, o1, o2, vo
     na = 1 << 27
+    hma, hmb = dg.merge_keys_u64(cpu_n // 2, 4), dg.merge_keys_u64(cpu_n // 2, 5)
+    hmva = np.arange(cpu_n // 2, dtype=np.uint32)
+    hmvb = hmva + np.uint32(cpu_n // 2)
     ka, kb = dev(dg.merge_keys_u64(na, 4)), dev(dg.merge_keys_u64(na, 5))
     va = torch.arange(na, dtype=torch.int32, device="cuda")
     vb = va + na
@@ -230,7 +256,8 @@ def bench_others(torch, tb, lib, peak):
     vo = torch.empty(2 * na, dtype=torch.int32, device="cuda")
     ws, need = ws_for("tb200_merge_by_key", None, None, na, None, None, na, None, None, 7, 4, 0)
     record("merge_by_key 2 x 2^27 (u64, u32)", 2 * na, 24,
-           lambda: lib.tb200_merge_by_key(p(ka), p(va), na, p(kb), p(vb), na, p(ko), p(vo), 7, 4, 0, p(ws), C.byref(need), st))
+           lambda: lib.tb200_merge_by_key(p(ka), p(va), na, p(kb), p(vb), na, p(ko), p(vo), 7, 4, 0, p(ws), C.byref(need), st),
+           cpu=cpu_time(lambda: ora.merge_by_key(hma, hmb, hmva, hmvb), cpu_n))
     del ka, kb, va, vb, ko, vo
     n64 = 1 << 27
     k0 = dev(dg.sort_keys_u64_40bit(n64))
@@ -256,7 +283,8 @@ def bench_others(torch, tb, lib, peak):
     ws, need = ws_for("tb200_merge_sort_by_key", None, None, None, None, nz, 5, 4, 0)
     passes = 1 + int(np.ceil(np.log2(nz / 4096)))
     record("stable_sort zip(u32,f32) by key 2^26, merge-sort route", nz, 16 * passes,
-           lambda: lib.tb200_merge_sort_by_key(p(k), p(kalt), p(v), p(valt), nz, 5, 4, 0, p(ws), C.byref(need), st), setup=restore2, reps=5)
+           lambda: lib.tb200_merge_sort_by_key(p(k), p(kalt), p(v), p(valt), nz, 5, 4, 0, p(ws), C.byref(need), st), setup=restore2, reps=5,
+           cpu=cpu_time(lambda: ora.stable_sort_zip_by_first(zk[:cpu_n], zv[:cpu_n].view(np.uint32)), cpu_n))
     ws, need = ws_for("tb200_sort_by_key", None, None, None, None, nz, 5, 4, 0, 0, 32)
     record("stable_sort zip(u32,f32) by key 2^26, radix route", nz, 68,
            lambda: lib.tb200_sort_by_key(p(k), p(kalt), p(v), p(valt), nz, 5, 4, 0, 0, 32, p(ws), C.byref(need), st), setup=restore2, reps=5)

@@ -71,7 +71,7 @@ int tb200_exclusive_scan(const void* d_in, void* d_out, size_t n, int t, int op,
  * or thrust::greater (descending=1) on arithmetic keys -- thrust/system/cuda/detail/sort.h:
  * 1621-1754, radix path :1438-1508.  Stable.  Sorts d_keys (and d_vals) in place; d_keys_alt /
  * d_vals_alt are caller-provided buffers of the same size that play the part of the reference's
- * double buffer (sort.h:1465-1484).  key_t: I32 U32 F32 I64 U64 F64.  val_bytes: 0 (keys only),
+ * double buffer (sort.h:1465-1484).  key_t: any of the ten dtypes.  val_bytes: 0 (keys only),
  * 4 or 8.  Only key bits [begin_bit, end_bit) are compared (multiples of 8; pass 0 and
  * 8*sizeof(key) for a full sort).  n < 2^31, as in the reference (sort.h:1346). */
 int tb200_sort_by_key(void* d_keys, void* d_keys_alt, void* d_vals, void* d_vals_alt, size_t n,

@@ -83,8 +83,10 @@ template <class K> struct radix_order<thrust::greater<K>, K> { static constexpr 
 template <class K> struct radix_order<thrust::greater<void>, K> { static constexpr int value = 1; };
 
 template <class K> struct radix_key {
-  static constexpr bool ok = std::is_arithmetic<K>::value && !std::is_same<K, bool>::value && (sizeof(K) == 4 || sizeof(K) == 8);
-  using bits = typename std::conditional<sizeof(K) == 4, std::uint32_t, unsigned long long>::type;
+  static constexpr bool ok = std::is_arithmetic<K>::value && !std::is_same<K, bool>::value && sizeof(K) <= 8;
+  using bits = typename std::conditional<sizeof(K) == 1, std::uint8_t,
+               typename std::conditional<sizeof(K) == 2, std::uint16_t,
+               typename std::conditional<sizeof(K) == 4, std::uint32_t, unsigned long long>::type>::type>::type;
   static constexpr int kind = std::is_floating_point<K>::value ? ::tb200::KEY_FLOAT : (std::is_signed<K>::value ? ::tb200::KEY_SIGNED : ::tb200::KEY_UNSIGNED);
 };
 

@@ -42,7 +42,7 @@ def test_size_queries_need_no_gpu():
     assert lib.tb200_sort_by_key(None, None, None, None, 1 << 20, 5, 4, 0, 0, 32, None, ctypes.byref(need), None) == 0
     assert need.value > (1 << 20) // 8192 * 1024
     assert lib.tb200_reduce(None, 8, 8, 4, 0, None, None, None, ctypes.byref(need), None) == 801       # f32 -> i32 unsupported
-    assert lib.tb200_sort_by_key(None, None, None, None, 8, 5, 3, 0, 0, 32, None, ctypes.byref(need), None) == 801
+    assert lib.tb200_sort_by_key(None, None, None, None, 8, 5, 3, 0, 0, 32, None, ctypes.byref(need), None) == 801    # 3-byte values
     assert lib.tb200_reduce(None, 8, 4, 6, 0, None, None, None, None, None) == 1                      # no size pointer
 
 

@@ -7,7 +7,8 @@ from thrust_b200 import datagen as dg
 from gpu_util import EDGE_SIZES, dev, host, rand_of
 
 pytestmark = pytest.mark.gpu
-KEY_TYPES = [np.int32, np.uint32, np.float32, np.int64, np.uint64, np.float64]
+KEY_TYPES = [np.int8, np.uint8, np.int16, np.uint16, np.int32, np.uint32, np.float32, np.int64, np.uint64, np.float64]
+WIDE_KEY_TYPES = KEY_TYPES[4:]
 
 
 @pytest.mark.parametrize("n", EDGE_SIZES)
@@ -102,7 +103,7 @@ def test_merge_sort_zip_by_first(tb, oracles, n):
 
 def test_merge_sort_types(tb, port):
     n = 50021
-    for dt in KEY_TYPES:
+    for dt in WIDE_KEY_TYPES:
         k = rand_of(dt, n, 55, small=True)
         v = np.arange(n, dtype=np.uint64)
         for desc in (False, True):

@@ -31,13 +31,16 @@ TB200_API int tb200_sort_by_key(void* d_keys, void* d_keys_alt, void* d_vals, vo
   tb200::key_coding coding;
   coding.descending = descending ? 1 : 0;
   switch (key_t) {
-    case TB200_U32: case TB200_U64: coding.kind = tb200::KEY_UNSIGNED; break;
-    case TB200_I32: case TB200_I64: coding.kind = tb200::KEY_SIGNED; break;
+    case TB200_U8: case TB200_U16: case TB200_U32: case TB200_U64: coding.kind = tb200::KEY_UNSIGNED; break;
+    case TB200_I8: case TB200_I16: case TB200_I32: case TB200_I64: coding.kind = tb200::KEY_SIGNED; break;
     case TB200_F32: case TB200_F64: coding.kind = tb200::KEY_FLOAT; break;
     default: return ERR_UNSUPPORTED;
   }
-  if (dtype_size(key_t) == 4)
-    return sort_by_val<uint32_t>(d_keys, d_keys_alt, d_vals, d_vals_alt, n, val_bytes, coding, begin_bit, end_bit, d_ws, ws_bytes, stream);
+  switch (dtype_size(key_t)) {
+    case 1: return sort_by_val<uint8_t>(d_keys, d_keys_alt, d_vals, d_vals_alt, n, val_bytes, coding, begin_bit, end_bit, d_ws, ws_bytes, stream);
+    case 2: return sort_by_val<uint16_t>(d_keys, d_keys_alt, d_vals, d_vals_alt, n, val_bytes, coding, begin_bit, end_bit, d_ws, ws_bytes, stream);
+    case 4: return sort_by_val<uint32_t>(d_keys, d_keys_alt, d_vals, d_vals_alt, n, val_bytes, coding, begin_bit, end_bit, d_ws, ws_bytes, stream);
+  }
   return sort_by_val<unsigned long long>(d_keys, d_keys_alt, d_vals, d_vals_alt, n, val_bytes, coding, begin_bit, end_bit, d_ws, ws_bytes, stream);
 }
 
