@@ -116,6 +116,23 @@ int tb200_reduce_by_key(const void* d_keys, const void* d_vals, void* d_keys_out
                         size_t n, int key_t, int val_t, int op, unsigned long long* d_count,
                         void* d_ws, size_t* ws_bytes, tb200_stream_t stream);
 
+/* thrust::inclusive_scan_by_key / exclusive_scan_by_key(keys, keys + n, vals, out, [init,] equal_to,
+ * op) -- thrust/system/cuda/detail/scan_by_key.h:172-588 (not one of the eight hot-path headers:
+ * the first of the "next" components).  The scan restarts at every run of equal keys; the
+ * exclusive form writes init at each run head.  key_t: any dtype; val_t: I32 U32 I64 U64 F32 F64.
+ * d_out may be d_vals.  n < 2^31. */
+int tb200_scan_by_key(const void* d_keys, const void* d_vals, void* d_out, size_t n, int key_t,
+                      int val_t, int op, int exclusive, const void* h_init, void* d_ws,
+                      size_t* ws_bytes, tb200_stream_t stream);
+
+/* thrust::unique_by_key_copy(keys, keys + n, vals, keys_out, vals_out) with equal_to --
+ * thrust/system/cuda/detail/unique_by_key.h:189-616: the first (key, value) of every run.
+ * val_bytes: 4 or 8.  *d_count = number of runs.  Outputs may alias the inputs (unique_by_key). */
+int tb200_unique_by_key_copy(const void* d_keys, const void* d_vals, void* d_keys_out,
+                             void* d_vals_out, size_t n, int key_t, int val_bytes,
+                             unsigned long long* d_count, void* d_ws, size_t* ws_bytes,
+                             tb200_stream_t stream);
+
 /* thrust::merge / thrust::merge_by_key(A, B, [payload A, payload B,] out, [payload out,] comp)
  * with thrust::less (descending=0) or thrust::greater (descending=1) --
  * thrust/system/cuda/detail/merge.h:862-1013.  Both inputs must already be sorted by comp.

@@ -47,6 +47,7 @@
 #include "reduce.cuh"
 #include "reduce_by_key.cuh"
 #include "scan.cuh"
+#include "scan_by_key.cuh"
 #include "select.cuh"
 
 THRUST_NAMESPACE_BEGIN
@@ -437,6 +438,73 @@ thrust::pair<KeyOutIt, ValOutIt> reduce_by_key(Policy& policy, KeyIt keys_first,
 template <class Policy, class KeyIt, class ValIt, class KeyOutIt, class ValOutIt, tb200_overlay::enable_for<Policy> = 0>
 thrust::pair<KeyOutIt, ValOutIt> reduce_by_key(Policy& policy, KeyIt keys_first, KeyIt keys_last, ValIt values_first, KeyOutIt keys_output, ValOutIt values_output) {
   return cuda_cub::reduce_by_key(policy, keys_first, keys_last, values_first, keys_output, values_output, thrust::equal_to<tb200_overlay::value_t<KeyIt>>());
+}
+
+// ------------------------------------------------------------------------------------- scan_by_key, unique_by_key
+// replaces cuda_cub::inclusive_scan_by_key / exclusive_scan_by_key (thrust/system/cuda/detail/scan_by_key.h)
+// and unique_by_key(_copy) (thrust/system/cuda/detail/unique_by_key.h): the first "next" components
+template <class Policy, class KeyIt, class ValIt, class OutIt, class BinaryPred, class ScanOp, tb200_overlay::enable_for<Policy> = 0>
+OutIt inclusive_scan_by_key(Policy& policy, KeyIt key_first, KeyIt key_last, ValIt value_first, OutIt value_result, BinaryPred binary_pred, ScanOp scan_op) {
+  namespace ov = tb200_overlay;
+  using K = ov::value_t<KeyIt>;
+  using V = ov::value_t<ValIt>;
+  const std::size_t n = (std::size_t)thrust::distance(key_first, key_last);
+  if (n == 0) return value_result;
+  ov::scratch<Policy> tmp(policy, ::tb200::scan_by_key_workspace_bytes<K, V>(n));
+  cudaError_t e = ::tb200::scan_by_key_async<true>(ov::unwrap(key_first), ov::unwrap(value_first), ov::unwrap(value_result), n, K(), V(), binary_pred,
+                                                 ov::map_op<ScanOp>::get(scan_op), tmp.at(), cuda_cub::stream(policy));
+  ov::finish(policy, e, tmp.at(), "inclusive_scan_by_key failed");
+  return value_result + n;
+}
+template <class Policy, class KeyIt, class ValIt, class OutIt, class BinaryPred, tb200_overlay::enable_for<Policy> = 0>
+OutIt inclusive_scan_by_key(Policy& policy, KeyIt key_first, KeyIt key_last, ValIt value_first, OutIt value_result, BinaryPred binary_pred) {
+  return cuda_cub::inclusive_scan_by_key(policy, key_first, key_last, value_first, value_result, binary_pred, thrust::plus<>());
+}
+template <class Policy, class KeyIt, class ValIt, class OutIt, tb200_overlay::enable_for<Policy> = 0>
+OutIt inclusive_scan_by_key(Policy& policy, KeyIt key_first, KeyIt key_last, ValIt value_first, OutIt value_result) {
+  return cuda_cub::inclusive_scan_by_key(policy, key_first, key_last, value_first, value_result, thrust::equal_to<>());
+}
+template <class Policy, class KeyIt, class ValIt, class OutIt, class Init, class BinaryPred, class ScanOp, tb200_overlay::enable_for<Policy> = 0>
+OutIt exclusive_scan_by_key(Policy& policy, KeyIt key_first, KeyIt key_last, ValIt value_first, OutIt value_result, Init init, BinaryPred binary_pred, ScanOp scan_op) {
+  namespace ov = tb200_overlay;
+  using K = ov::value_t<KeyIt>;
+  using V = Init;                                                                       // accumulates in the init type
+  const std::size_t n = (std::size_t)thrust::distance(key_first, key_last);
+  if (n == 0) return value_result;
+  ov::scratch<Policy> tmp(policy, ::tb200::scan_by_key_workspace_bytes<K, V>(n));
+  cudaError_t e = ::tb200::scan_by_key_async<false>(ov::unwrap(key_first), ov::unwrap(value_first), ov::unwrap(value_result), n, K(), init, binary_pred,
+                                                  ov::map_op<ScanOp>::get(scan_op), tmp.at(), cuda_cub::stream(policy));
+  ov::finish(policy, e, tmp.at(), "exclusive_scan_by_key failed");
+  return value_result + n;
+}
+template <class Policy, class KeyIt, class ValIt, class OutIt, class Init, class BinaryPred, tb200_overlay::enable_for<Policy> = 0>
+OutIt exclusive_scan_by_key(Policy& policy, KeyIt key_first, KeyIt key_last, ValIt value_first, OutIt value_result, Init init, BinaryPred binary_pred) {
+  return cuda_cub::exclusive_scan_by_key(policy, key_first, key_last, value_first, value_result, init, binary_pred, thrust::plus<>());
+}
+template <class Policy, class KeyIt, class ValIt, class OutIt, class Init, tb200_overlay::enable_for<Policy> = 0>
+OutIt exclusive_scan_by_key(Policy& policy, KeyIt key_first, KeyIt key_last, ValIt value_first, OutIt value_result, Init init) {
+  return cuda_cub::exclusive_scan_by_key(policy, key_first, key_last, value_first, value_result, init, thrust::equal_to<>());
+}
+template <class Policy, class KeyIt, class ValIt, class OutIt, tb200_overlay::enable_for<Policy> = 0>
+OutIt exclusive_scan_by_key(Policy& policy, KeyIt key_first, KeyIt key_last, ValIt value_first, OutIt value_result) {
+  return cuda_cub::exclusive_scan_by_key(policy, key_first, key_last, value_first, value_result, tb200_overlay::value_t<ValIt>{});
+}
+template <class Policy, class KeyIt, class ValIt, class KeyOutIt, class ValOutIt, class BinaryPred, tb200_overlay::enable_for<Policy> = 0>
+thrust::pair<KeyOutIt, ValOutIt> unique_by_key_copy(Policy& policy, KeyIt keys_first, KeyIt keys_last, ValIt values_first, KeyOutIt keys_result, ValOutIt values_result,
+                                                    BinaryPred binary_pred) {
+  return cuda_cub::reduce_by_key(policy, keys_first, keys_last, values_first, keys_result, values_result, binary_pred, ::tb200::first_op());
+}
+template <class Policy, class KeyIt, class ValIt, class KeyOutIt, class ValOutIt, tb200_overlay::enable_for<Policy> = 0>
+thrust::pair<KeyOutIt, ValOutIt> unique_by_key_copy(Policy& policy, KeyIt keys_first, KeyIt keys_last, ValIt values_first, KeyOutIt keys_result, ValOutIt values_result) {
+  return cuda_cub::unique_by_key_copy(policy, keys_first, keys_last, values_first, keys_result, values_result, thrust::equal_to<tb200_overlay::value_t<KeyIt>>());
+}
+template <class Policy, class KeyIt, class ValIt, class BinaryPred, tb200_overlay::enable_for<Policy> = 0>
+thrust::pair<KeyIt, ValIt> unique_by_key(Policy& policy, KeyIt keys_first, KeyIt keys_last, ValIt values_first, BinaryPred binary_pred) {
+  return cuda_cub::unique_by_key_copy(policy, keys_first, keys_last, values_first, keys_first, values_first, binary_pred);
+}
+template <class Policy, class KeyIt, class ValIt, tb200_overlay::enable_for<Policy> = 0>
+thrust::pair<KeyIt, ValIt> unique_by_key(Policy& policy, KeyIt keys_first, KeyIt keys_last, ValIt values_first) {
+  return cuda_cub::unique_by_key(policy, keys_first, keys_last, values_first, thrust::equal_to<tb200_overlay::value_t<KeyIt>>());
 }
 
 // ------------------------------------------------------------------------------------- merge

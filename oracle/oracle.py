@@ -49,7 +49,7 @@ class Oracle:
         lib.ora_kind.restype = C.c_char_p
         lib.ora_threads.restype = C.c_int
         for name in ("ora_copy_if", "ora_partition", "ora_stable_partition", "ora_partition_copy",
-                     "ora_unique_copy", "ora_reduce_by_key", "ora_reduce_by_key_f32_via_f64"):
+                     "ora_unique_copy", "ora_reduce_by_key", "ora_reduce_by_key_f32_via_f64", "ora_unique_by_key_copy"):
             getattr(lib, name).restype = C.c_int64
         self.kind = lib.ora_kind().decode()
         self.threads = lib.ora_threads()
@@ -161,6 +161,25 @@ class Oracle:
         vo = np.empty_like(v)
         n = self.lib.ora_reduce_by_key_f32_via_f64(_ptr(k), _ptr(v), _ptr(ko), _ptr(vo),
                                                    C.c_size_t(k.size), DTYPES[k.dtype])
+        return ko[:n].copy(), vo[:n].copy()
+
+    def scan_by_key(self, keys, vals, op="plus", exclusive=False, init=0):
+        k = np.ascontiguousarray(keys)
+        v = np.ascontiguousarray(vals)
+        out = np.empty_like(v)
+        i0 = np.asarray(init, dtype=v.dtype)
+        rc = self.lib.ora_scan_by_key(_ptr(k), _ptr(v), _ptr(out), C.c_size_t(k.size), DTYPES[k.dtype], DTYPES[v.dtype], OPS[op],
+                                      int(exclusive), _ptr(i0))
+        assert rc == 0
+        return out
+
+    def unique_by_key_copy(self, keys, vals):
+        k = np.ascontiguousarray(keys)
+        v = np.ascontiguousarray(vals)
+        ko = np.empty_like(k)
+        vo = np.empty_like(v)
+        n = self.lib.ora_unique_by_key_copy(_ptr(k), _ptr(v), _ptr(ko), _ptr(vo), C.c_size_t(k.size), DTYPES[k.dtype], v.dtype.itemsize)
+        assert n >= 0
         return ko[:n].copy(), vo[:n].copy()
 
     # -- merge ---------------------------------------------------------------------------------

@@ -81,6 +81,16 @@ int64_t ora_reduce_by_key(const void* keys, const void* vals, void* keys_out, vo
 int64_t ora_reduce_by_key_f32_via_f64(const void* keys, const float* vals, void* keys_out,
                                       float* vals_out, size_t n, int key_t);
 
+/* thrust::inclusive_scan_by_key / exclusive_scan_by_key(keys, vals, out, [init,] equal_to, op): the
+ * scan restarts at every run of equal keys.  val_t: I32 U32 I64 U64 F32 F64; out may be vals. */
+int ora_scan_by_key(const void* keys, const void* vals, void* out, size_t n, int key_t, int val_t,
+                    int op, int exclusive, const void* init);
+
+/* thrust::unique_by_key_copy(keys, vals, keys_out, vals_out) with equal_to: first (key, value) of
+ * every run.  val_bytes in {4, 8}. -> number of runs */
+int64_t ora_unique_by_key_copy(const void* keys, const void* vals, void* keys_out, void* vals_out,
+                               size_t n, int key_t, int val_bytes);
+
 /* thrust::merge / thrust::merge_by_key with less (or greater when descending=1); ties take
  * from range A first.  val_bytes in {0, 4, 8}. */
 int ora_merge_by_key(const void* ka, const void* va, size_t na, const void* kb, const void* vb,

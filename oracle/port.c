@@ -378,6 +378,61 @@ ORA_EXPORT int64_t ora_reduce_by_key_f32_via_f64(const void* keys, const float* 
   return runs;
 }
 
+/* ---------------------------------------------------------------- scan_by_key, unique_by_key
+ * The scan restarts wherever key[i] != key[i-1] (thrust/system/detail/generic/scan_by_key.inl:
+ * 103-131 builds head flags this way and scans (value, flag) pairs with segmented_scan_functor,
+ * :43-61; the exclusive form, :198-234, seeds every run with init).  Left to right in the value
+ * type. */
+#define SBK_VAL_CASE(code, V, sfx)                                                     \
+  if (val_t == code) {                                                                 \
+    const V* v = (const V*)vals; V* o = (V*)out; V i0 = 0; V acc = 0;                  \
+    if (exclusive) memcpy(&i0, init, sizeof(V));                                       \
+    for (size_t i = 0; i < n; ++i) {                                                   \
+      const char* kp = (const char*)keys + i * ks;                                     \
+      int head = i == 0 || !key_eq(kp, kp - ks, key_t);                                \
+      V x = v[i];                                                                      \
+      if (exclusive) {                                                                 \
+        if (head) acc = i0;                                                            \
+        o[i] = acc;                                                                    \
+        if (op == ORA_PLUS) acc = (V)(acc + x);                                        \
+        else if (op == ORA_MIN) acc = x < acc ? x : acc;                               \
+        else acc = acc < x ? x : acc;                                                  \
+      } else {                                                                         \
+        if (head) acc = x;                                                             \
+        else if (op == ORA_PLUS) acc = (V)(acc + x);                                   \
+        else if (op == ORA_MIN) acc = x < acc ? x : acc;                               \
+        else acc = acc < x ? x : acc;                                                  \
+        o[i] = acc;                                                                    \
+      }                                                                                \
+    }                                                                                  \
+    return 0;                                                                          \
+  }
+ORA_EXPORT int ora_scan_by_key(const void* keys, const void* vals, void* out, size_t n, int key_t,
+                               int val_t, int op, int exclusive, const void* init) {
+  size_t ks = dtype_size(key_t);
+  if (!ks) return -1;
+  FOR_WIDE_TYPES(SBK_VAL_CASE)
+  return -1;
+}
+
+/* unique_by_key_copy keeps the first (key, value) of every run
+ * (thrust/system/detail/generic/unique_by_key.inl: unique_by_key_copy with equal_to). */
+ORA_EXPORT int64_t ora_unique_by_key_copy(const void* keys, const void* vals, void* keys_out,
+                                          void* vals_out, size_t n, int key_t, int val_bytes) {
+  size_t ks = dtype_size(key_t), vs = (size_t)val_bytes;
+  int64_t cnt = 0;
+  if (!ks || !vs) return -1;
+  for (size_t i = 0; i < n; ++i) {
+    const char* kp = (const char*)keys + i * ks;
+    if (i == 0 || !key_eq(kp, kp - ks, key_t)) {
+      memmove((char*)keys_out + (size_t)cnt * ks, kp, ks);
+      memmove((char*)vals_out + (size_t)cnt * vs, (const char*)vals + i * vs, vs);
+      ++cnt;
+    }
+  }
+  return cnt;
+}
+
 /* ---------------------------------------------------------------- merge
  * Sequential two-finger merge; on equal keys the element of range A is emitted first
  * (thrust/system/detail/sequential/merge.inl:36-76 and :85-140: "if comp(*first2, *first1) take

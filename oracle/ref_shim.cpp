@@ -14,6 +14,7 @@
 #include <thrust/partition.h>
 #include <thrust/unique.h>
 #include <thrust/merge.h>
+#include <thrust/scan.h>
 #include <thrust/functional.h>
 #include <thrust/iterator/zip_iterator.h>
 #include <thrust/tuple.h>
@@ -293,6 +294,41 @@ ORA_EXPORT int64_t ora_reduce_by_key_f32_via_f64(const void* keys, const float* 
     if (n) vals_out[runs - 1] = (float)acc;
   });
   return runs;
+}
+
+ORA_EXPORT int ora_scan_by_key(const void* keys, const void* vals, void* out, size_t n, int key_t, int val_t, int op,
+                               int exclusive, const void* init) {
+  int rc = -1;
+  by_dtype(key_t, [&](auto kv) {
+    using K = decltype(kv);
+    const K* k = static_cast<const K*>(keys);
+    rc = by_wide_dtype(val_t, [&](auto vv) {
+      using V = decltype(vv);
+      const V* v = static_cast<const V*>(vals); V* o = static_cast<V*>(out);
+      V i0 = V(); if (exclusive) std::memcpy(&i0, init, sizeof(V));
+      auto run = [&](auto f) {
+        if (exclusive) thrust::exclusive_scan_by_key(thrust::device, k, k + n, v, o, i0, thrust::equal_to<K>(), f);
+        else thrust::inclusive_scan_by_key(thrust::device, k, k + n, v, o, thrust::equal_to<K>(), f);
+      };
+      if (op == ORA_PLUS) run(thrust::plus<V>()); else if (op == ORA_MIN) run(min_op<V>()); else run(max_op<V>());
+    });
+  });
+  return rc;
+}
+
+ORA_EXPORT int64_t ora_unique_by_key_copy(const void* keys, const void* vals, void* keys_out, void* vals_out, size_t n,
+                                          int key_t, int val_bytes) {
+  int64_t cnt = -1;
+  by_dtype(key_t, [&](auto kv) {
+    using K = decltype(kv);
+    const K* k = static_cast<const K*>(keys); K* ko = static_cast<K*>(keys_out);
+    by_bytes(val_bytes, [&](auto vv) {
+      using V = decltype(vv);
+      const V* v = static_cast<const V*>(vals); V* vo = static_cast<V*>(vals_out);
+      cnt = thrust::unique_by_key_copy(thrust::device, k, k + n, v, ko, vo).first - ko;
+    });
+  });
+  return cnt;
 }
 
 ORA_EXPORT int ora_merge_by_key(const void* ka, const void* va, size_t na, const void* kb,

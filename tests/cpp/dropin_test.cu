@@ -17,6 +17,7 @@
 #include <thrust/partition.h>
 #include <thrust/reduce.h>
 #include <thrust/scan.h>
+#include <thrust/sequence.h>
 #include <thrust/sort.h>
 #include <thrust/tuple.h>
 #include <thrust/unique.h>
@@ -123,6 +124,17 @@ int main() {
   auto uin = thrust::unique(thrust::device, dr.begin(), dr.end());                          // in place
   CHECK((uin - dr.begin()) == runs.back() + 1);
 
+  // the first "next" components: scan_by_key and unique_by_key
+  { thrust::device_vector<int> dkeys(runs.begin(), runs.end()), dones(n, 1), dsk(n);
+    thrust::inclusive_scan_by_key(thrust::device, dkeys.begin(), dkeys.end(), dones.begin(), dsk.begin());
+    got = dsk; ok = true; { int c = 0; for (int i = 0; i < n && ok; ++i) { c = (i && runs[i] == runs[i - 1]) ? c + 1 : 1; ok = got[i] == c; } } CHECK(ok);
+    thrust::exclusive_scan_by_key(thrust::device, dkeys.begin(), dkeys.end(), dones.begin(), dsk.begin(), 10);
+    got = dsk; ok = true; { int c = 0; for (int i = 0; i < n && ok; ++i) { c = (i && runs[i] == runs[i - 1]) ? c + 1 : 0; ok = got[i] == 10 + c; } } CHECK(ok);
+    thrust::device_vector<int> dpos(n); thrust::sequence(dpos.begin(), dpos.end());
+    auto ue = thrust::unique_by_key(thrust::device, dkeys.begin(), dkeys.end(), dpos.begin());
+    CHECK((ue.first - dkeys.begin()) == runs.back() + 1);
+    got = dpos; ok = true; { int r = 0; for (int i = 0; i < n && ok; ++i) if (i == 0 || runs[i] != runs[i - 1]) { ok = got[r] == i; ++r; } } CHECK(ok); }
+
   // merge_by_key: ties take from the first range
   { int na = 300007, nb = 200003; std::vector<unsigned long long> a(na), b(nb); for (int i = 0; i < na; ++i) a[i] = mix(i) >> 52; for (int i = 0; i < nb; ++i) b[i] = mix(i + na) >> 52;
     std::sort(a.begin(), a.end()); std::sort(b.begin(), b.end());
@@ -140,7 +152,7 @@ int main() {
 
   // the overlay, not the stock CUB path, served these calls
   std::printf("overlay served %llu calls\n", thrust::cuda_cub::tb200_overlay::call_count());
-  CHECK(thrust::cuda_cub::tb200_overlay::call_count() == 21);
+  CHECK(thrust::cuda_cub::tb200_overlay::call_count() == 24);
   cudaStreamDestroy(s);
   if (cudaDeviceSynchronize() != cudaSuccess) { std::printf("FAILED: sticky CUDA error\n"); ++failures; }
   std::printf(failures ? "dropin_test: %d FAILURES\n" : "dropin_test: all checks passed\n", failures);

@@ -189,3 +189,31 @@ def test_reference_fp32_scan_drifts(port):
     yard = port.scan_f32_via_f64(x)
     rel = abs(float(seq[-1]) - float(yard[-1])) / float(yard[-1])
     assert 1e-7 < rel < 1e-3
+
+
+@pytest.mark.parametrize("n", SIZES)
+def test_port_vs_ref_by_key(port, ref, n):
+    """scan_by_key and unique_by_key_copy (the first of the "next" components): restatement vs reference."""
+    for kt in (np.int32, np.uint8, np.int64, np.float32):
+        keys = rand_of(kt, n, 41, small=True)
+        for vt in WIDE_TYPES:
+            vals = rand_of(vt, n, 42, small=True)
+            for op in ("plus", "min", "max"):
+                assert np.array_equal(port.scan_by_key(keys, vals, op), ref.scan_by_key(keys, vals, op)), (kt, vt, op)
+                assert np.array_equal(port.scan_by_key(keys, vals, op, True, 3), ref.scan_by_key(keys, vals, op, True, 3)), (kt, vt, op)
+        for vt in (np.uint32, np.uint64):
+            vals = np.arange(n, dtype=vt)
+            pk, pv = port.unique_by_key_copy(keys, vals)
+            rk, rv = ref.unique_by_key_copy(keys, vals)
+            assert np.array_equal(pk, rk) and np.array_equal(pv, rv), (kt, vt)
+
+
+def test_known_answers_by_key(oracles):
+    # the worked example of the reference's documentation, thrust/scan.h (inclusive_scan_by_key / exclusive_scan_by_key)
+    keys = np.array([0, 0, 0, 1, 1, 2, 3, 3, 3, 3], np.int32)
+    ones = np.ones(10, np.int32)
+    for o in oracles:
+        assert o.scan_by_key(keys, ones).tolist() == [1, 2, 3, 1, 2, 1, 1, 2, 3, 4]
+        assert o.scan_by_key(keys, ones, "plus", True, 5).tolist() == [5, 6, 7, 5, 6, 5, 5, 6, 7, 8]
+        k, v = o.unique_by_key_copy(np.array([1, 3, 3, 3, 2, 2, 1], np.int32), np.array([9, 8, 7, 6, 5, 4, 3], np.uint32))
+        assert k.tolist() == [1, 3, 2, 1] and v.tolist() == [9, 8, 5, 3]

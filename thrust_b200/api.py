@@ -241,6 +241,45 @@ def reduce_by_key(keys, vals, op="plus"):
     return ko[:k], vo[:k]
 
 
+def inclusive_scan_by_key(keys, vals, out=None, op="plus"):
+    """thrust::inclusive_scan_by_key(keys_first, keys_last, values_first, result, equal_to, op)."""
+    _require_cuda(keys, vals, out)
+    out = torch.empty_like(vals) if out is None else out
+    ws = _call_with_ws("rbk", "tb200_scan_by_key", _ptr(keys), _ptr(vals), _ptr(out), keys.numel(), DTYPE_CODE[keys.dtype],
+                       DTYPE_CODE[vals.dtype], OPS[op], 0, None)
+    _sync_and_check(ws, "inclusive_scan_by_key")
+    return out
+
+
+def exclusive_scan_by_key(keys, vals, init=0, out=None, op="plus"):
+    """thrust::exclusive_scan_by_key(keys_first, keys_last, values_first, result, init, equal_to, op)."""
+    _require_cuda(keys, vals, out)
+    out = torch.empty_like(vals) if out is None else out
+    h_init = np.asarray(init, dtype=NP_OF[vals.dtype])
+    ws = _call_with_ws("rbk", "tb200_scan_by_key", _ptr(keys), _ptr(vals), _ptr(out), keys.numel(), DTYPE_CODE[keys.dtype],
+                       DTYPE_CODE[vals.dtype], OPS[op], 1, C.c_void_p(h_init.ctypes.data))
+    _sync_and_check(ws, "exclusive_scan_by_key")
+    return out
+
+
+def unique_by_key_copy(keys, vals, keys_out=None, vals_out=None):
+    """thrust::unique_by_key_copy: returns (keys_out[:runs], vals_out[:runs])."""
+    _require_cuda(keys, vals, keys_out, vals_out)
+    ko = torch.empty_like(keys) if keys_out is None else keys_out
+    vo = torch.empty_like(vals) if vals_out is None else vals_out
+    cnt = _count_word()
+    ws = _call_with_ws("rbk", "tb200_unique_by_key_copy", _ptr(keys), _ptr(vals), _ptr(ko), _ptr(vo), keys.numel(),
+                       DTYPE_CODE[keys.dtype], vals.element_size(), _ptr(cnt))
+    _sync_and_check(ws, "unique_by_key_copy")
+    k = _read_count(cnt)
+    return ko[:k], vo[:k]
+
+
+def unique_by_key(keys, vals):
+    """thrust::unique_by_key in place: returns (keys[:runs], vals[:runs])."""
+    return unique_by_key_copy(keys, vals, keys, vals)
+
+
 # ------------------------------------------------------------------------------------- merge
 def merge_by_key(keys_a, keys_b, vals_a=None, vals_b=None, descending=False, sync=True):
     """thrust::merge_by_key(A, B, payload A, payload B, keys_out, payload_out[, greater]); with no
