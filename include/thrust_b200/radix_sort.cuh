@@ -7,10 +7,13 @@
 //   2. radix_scan_hist_kernel exclusive-scans each histogram into bucket bases and marks a digit
 //                             place as skippable when one bucket holds every key;
 //   3. onesweep_kernel        once per non-skipped digit place: a tile of keys is ranked inside
-//                             the CTA (warp ballots + per-warp counters), the tile's per-digit
-//                             counts are chained to the preceding tiles by decoupled look-back
-//                             (one thread per digit), and keys then values are staged through
+//                             the CTA (warp ballots, match.any for a third of the keys, per-warp
+//                             counters), the tile's per-digit counts are published, the keys are
+//                             staged in shared memory, then the counts are chained to the
+//                             preceding tiles by decoupled look-back (one thread per digit, four
+//                             descriptors fetched per round trip), and keys then values leave
 //                             shared memory so that each bucket's run is written contiguously;
+//                             each CTA also asks L2 for the tile the next wave will take;
 //   4. radix_copy_back_kernel only if an odd number of places ran: moves the result from the
 //                             alternate buffer to the caller's.
 // A pass therefore reads and writes each key (and value) exactly once.  The sort is stable.
@@ -157,6 +160,7 @@ template <int KB, int VB> struct onesweep_tuning {
 // up to 256 bins and where a bin's items go.
 template <class UK, class UV, bool IS_FLOAT> struct radix_pass_policy {
   static constexpr int BITS = RADIX_BITS;       // ballots per key
+  static constexpr int MATCH_EVERY = 3;         // every third key is ranked with match.any instead
   UK* dst; UV* vdst; int shift; unsigned dmask;
   __device__ __forceinline__ unsigned digit(UK k) const { return key_digit<IS_FLOAT>(k, shift, dmask); }
   __device__ __forceinline__ UK* keys_of(unsigned) const { return dst; }
@@ -177,6 +181,7 @@ constexpr int MAX_BUCKETS = 16;
 // may be a buffer in another GPU's memory (ordinary stores over NVLink)
 template <class UK, class UV> struct bucket_policy {
   static constexpr int BITS = 4;
+  static constexpr int MATCH_EVERY = 0;
   key_coding coding; int buckets;
   const UK* split_code;      // shared memory: buckets - 1 codes, ascending
   UK* const* dst_k; UV* const* dst_v;   // shared memory tables of destination pointers
@@ -220,16 +225,22 @@ __device__ __forceinline__ void onesweep_tile(const UK* __restrict__ src, const 
   for (int i = 0; i < IPT; ++i) {
     // a partial tile pads with pseudo-keys of the highest digit: ranked after every real key of the tile
     unsigned d = (FULL || wofs + i * 32 < tile_n) ? policy.digit(key[i]) : (unsigned)PAD_DIGIT;
-    // lanes holding the same digit: one ballot per digit bit.  (match.any computes this in one
-    // instruction but is issued at a small fraction of the ballot rate on sm_100.)
-    unsigned peers = FULL_MASK;
+    // lanes holding the same digit: one ballot per digit bit.  Every MATCH_EVERY-th key asks the
+    // match unit instead: it runs beside the ALU pipe that the ballots load, but at a small fraction
+    // of their rate on sm_100, so it can only take a share of the keys.
+    unsigned peers;
+    if (Policy::MATCH_EVERY != 0 && (i + 1) % (Policy::MATCH_EVERY != 0 ? Policy::MATCH_EVERY : 1) == 0) {
+      peers = __match_any_sync(FULL_MASK, d);
+    } else {
+      peers = FULL_MASK;
 #pragma unroll
-    for (int b = 0; b < Policy::BITS; ++b) {
-      const bool bit = (d >> b) & 1;
-      const unsigned vote = __ballot_sync(FULL_MASK, bit);
-      peers &= bit ? vote : ~vote;
+      for (int b = 0; b < Policy::BITS; ++b) {
+        const bool bit = (d >> b) & 1;
+        const unsigned vote = __ballot_sync(FULL_MASK, bit);
+        peers &= bit ? vote : ~vote;
+      }
     }
-    unsigned ahead = __popc(peers & lanemask_lt);
+    const unsigned ahead = __popc(peers & lanemask_lt);
     unsigned before = 0;
     if (ahead == 0) before = atomicAdd(&my_hist[d], (unsigned)__popc(peers));
     before = __shfl_sync(FULL_MASK, before, __ffs(peers) - 1);
@@ -249,33 +260,14 @@ __device__ __forceinline__ void onesweep_tile(const UK* __restrict__ src, const 
     digit_off = incl - my_count;
   }
   __syncthreads();
+  unsigned real_count = 0;
+  LB* const slot = lookback + (size_t)tile * RADIX_BINS + (threadIdx.x & (RADIX_BINS - 1));
   if (threadIdx.x < RADIX_BINS) {
     for (int w = 0; w < warp; ++w) digit_off += s_scan[w];
-    unsigned real_count = my_count;
+    real_count = my_count;
     if (!FULL && threadIdx.x == PAD_DIGIT) real_count -= (unsigned)TILE - tile_n;
-    LB* slot = lookback + (size_t)tile * RADIX_BINS + threadIdx.x;
-    LB prefix = 0;
-    if (tile == 0) {
-      *reinterpret_cast<volatile LB*>(slot) = ((LB)TILE_INCLUSIVE << LB_BITS) | (LB)real_count;
-    } else {
-      *reinterpret_cast<volatile LB*>(slot) = ((LB)TILE_AGGREGATE << LB_BITS) | (LB)real_count;
-      const volatile LB* look = slot - RADIX_BINS;
-      unsigned iter = 0;
-      while (true) {
-        LB w = *look;
-        unsigned st = (unsigned)(w >> LB_BITS);
-        if (st == TILE_INVALID) {
-          if (++iter > SPIN_LIMIT) { record_error(err, ERR_LOOKBACK_TIMEOUT); break; }
-          backoff(iter);
-          continue;
-        }
-        prefix += w & LB_MASK;
-        if (st == TILE_INCLUSIVE) break;
-        look -= RADIX_BINS; iter = 0;
-      }
-      *reinterpret_cast<volatile LB*>(slot) = ((LB)TILE_INCLUSIVE << LB_BITS) | (LB)(prefix + real_count);
-    }
-    s_goff[threadIdx.x] = (unsigned)bin_base[threadIdx.x] + (unsigned)prefix - digit_off;
+    // the tile's own count is visible to its successors before anything else happens
+    *reinterpret_cast<volatile LB*>(slot) = ((LB)(tile == 0 ? TILE_INCLUSIVE : TILE_AGGREGATE) << LB_BITS) | (LB)real_count;
 #pragma unroll
     for (int w = 0; w < NWARPS; ++w) warp_hist[w * RADIX_BINS + threadIdx.x] += digit_off;
   }
@@ -293,6 +285,46 @@ __device__ __forceinline__ void onesweep_tile(const UK* __restrict__ src, const 
     const UV* vs = vsrc + tile_base + wofs;
 #pragma unroll
     for (int i = 0; i < IPT; ++i) val[i] = (FULL || wofs + i * 32 < tile_n) ? __ldcs(vs + i * 32) : (UV)0;
+  }
+
+  // ---- chain to the preceding tiles, one thread per digit.  The preceding tiles had the time of
+  // the staging above to publish; their descriptors are fetched LB_BATCH at a time so that the walk
+  // back to the nearest inclusive prefix costs one memory round trip per batch, not per tile.
+  if (threadIdx.x < RADIX_BINS) {
+    LB prefix = 0;
+    if (tile != 0) {
+      constexpr int LB_BATCH = 4;   // 2..6 measured alike, 8 and 16 slower
+      long long t = (long long)tile - 1;   // nearest tile not yet accounted for
+      unsigned iter = 0;
+      bool done = false;
+      while (!done) {
+        LB w[LB_BATCH];
+#pragma unroll
+        for (int j = 0; j < LB_BATCH; ++j) {
+          const long long tj = t - j > 0 ? t - j : 0;
+          w[j] = *reinterpret_cast<const volatile LB*>(lookback + (size_t)tj * RADIX_BINS + threadIdx.x);
+        }
+        bool stop = false;
+        int taken = 0;
+#pragma unroll
+        for (int j = 0; j < LB_BATCH; ++j) {
+          const unsigned st = (unsigned)(w[j] >> LB_BITS);
+          const bool take = !stop && st != TILE_INVALID;
+          if (take) { prefix += w[j] & LB_MASK; ++taken; }
+          if (take && st == TILE_INCLUSIVE) done = true;
+          stop = stop || st == TILE_INVALID || st == TILE_INCLUSIVE;
+        }
+        t -= taken;
+        if (taken == 0) {
+          if (++iter > SPIN_LIMIT) { record_error(err, ERR_LOOKBACK_TIMEOUT); break; }
+          backoff(iter);
+        } else {
+          iter = 0;
+        }
+      }
+      *reinterpret_cast<volatile LB*>(slot) = ((LB)TILE_INCLUSIVE << LB_BITS) | (LB)(prefix + real_count);
+    }
+    s_goff[threadIdx.x] = (unsigned)bin_base[threadIdx.x] + (unsigned)prefix - digit_off;
   }
   __syncthreads();
   // consecutive threads take consecutive staged slots, so each bucket's run is written contiguously
@@ -323,7 +355,7 @@ __device__ __forceinline__ void onesweep_tile(const UK* __restrict__ src, const 
 template <class UK, class UV, bool HAS_V, bool IS_FLOAT, class LB, int IPT>
 __global__ void __launch_bounds__(ONESWEEP_BLOCK, 2)
 onesweep_kernel(UK* buf_a, UK* buf_b, UV* val_a, UV* val_b, unsigned n, key_coding coding, int pass, int first_pass,
-                radix_ctrl* ctrl, LB* lookback, ws_header* hdr) {
+                radix_ctrl* ctrl, LB* lookback, ws_header* hdr, unsigned prefetch_tiles) {
   constexpr int NWARPS = ONESWEEP_BLOCK / 32;
   constexpr int TILE = ONESWEEP_BLOCK * IPT;
   if (ctrl->skip[pass]) return;
@@ -346,6 +378,17 @@ onesweep_kernel(UK* buf_a, UK* buf_b, UV* val_a, UV* val_b, unsigned n, key_codi
   for (int i = threadIdx.x; i < NWARPS * RADIX_BINS; i += ONESWEEP_BLOCK) warp_hist[i] = 0;
   __syncthreads();
   const unsigned tile = s_tile;
+  // Ask L2 for the tile that a CTA of the next wave will take, so that its loads find the data
+  // on chip.  (A hint only: needs a 16-byte aligned address, skipped otherwise.)
+  if (threadIdx.x == 32 && prefetch_tiles != 0) {
+    const unsigned long long ahead = (unsigned long long)(tile + prefetch_tiles) * TILE;
+    if (ahead + TILE <= n) {
+      if ((reinterpret_cast<unsigned long long>(src + ahead) & 15) == 0)
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src + ahead), "r"((unsigned)(TILE * sizeof(UK))) : "memory");
+      if (HAS_V && (reinterpret_cast<unsigned long long>(vsrc + ahead) & 15) == 0)
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(vsrc + ahead), "r"((unsigned)(TILE * sizeof(UV))) : "memory");
+    }
+  }
   const int shift = pass * RADIX_BITS;
   const unsigned dmask = digit_mask<UK>(coding, shift);
   const bool full = (unsigned long long)(tile + 1) * TILE <= n;
@@ -499,15 +542,16 @@ cudaError_t radix_sort_async(UK* keys_a, UK* keys_b, UV* vals_a, UV* vals_b, siz
   auto k64 = isf ? onesweep_kernel<UK, UV, HAS_V, true, unsigned long long, IPT> : onesweep_kernel<UK, UV, HAS_V, false, unsigned long long, IPT>;
   // opting in to large dynamic shared memory is per kernel and per device; it is cheap, so do it every call
   if ((e = cudaFuncSetAttribute(lb32 ? (const void*)k32 : (const void*)k64, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
+  const unsigned prefetch_tiles = 2u * (unsigned)di.sm_count;   // two CTAs are resident per SM: the next wave's tile
   for (int p = 0; p < num_passes; ++p) {
     char* lb = lb0 + lb_bytes * p;
     timed_launch tl(KID_ONESWEEP, stream);
     if (lb32)
       k32<<<(unsigned)tiles, ONESWEEP_BLOCK, smem, stream>>>(keys_a, keys_b, vals_a, vals_b, (unsigned)n, coding, first_pass + p, first_pass, ctrl,
-                                                            reinterpret_cast<uint32_t*>(lb), hdr);
+                                                            reinterpret_cast<uint32_t*>(lb), hdr, prefetch_tiles);
     else
       k64<<<(unsigned)tiles, ONESWEEP_BLOCK, smem, stream>>>(keys_a, keys_b, vals_a, vals_b, (unsigned)n, coding, first_pass + p, first_pass, ctrl,
-                                                            reinterpret_cast<unsigned long long*>(lb), hdr);
+                                                            reinterpret_cast<unsigned long long*>(lb), hdr, prefetch_tiles);
   }
   size_t cb_grid = (n + 256 * 8 - 1) / (256 * 8);
   if (cb_grid > (size_t)di.sm_count * 8) cb_grid = (size_t)di.sm_count * 8;

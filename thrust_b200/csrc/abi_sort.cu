@@ -43,4 +43,3 @@ TB200_API int tb200_sort_by_key(void* d_keys, void* d_keys_alt, void* d_vals, vo
   }
   return sort_by_val<unsigned long long>(d_keys, d_keys_alt, d_vals, d_vals_alt, n, val_bytes, coding, begin_bit, end_bit, d_ws, ws_bytes, stream);
 }
-
