@@ -244,7 +244,23 @@ def bench_others(torch, tb, lib, peak):
     record("reduce_by_key int32/fp32 runs(mean 4) 2^28", n, 10,
            lambda: lib.tb200_reduce_by_key(p(keys), p(vals), p(o1), p(vo), n, 4, 8, 0, p(cnt), p(ws2), C.byref(need2), st),
            cpu=cpu_time(lambda: ora.reduce_by_key(hk, hv), cpu_n))
-    del keys, vals, o1, o2, vo
+    # the "next" components built so far: scan_by_key, unique_by_key, minmax_element
+    ws3, need3 = ws_for("tb200_scan_by_key", None, None, None, n, 4, 8, 0, 0, None)
+    record("inclusive_scan_by_key int32/fp32 runs(mean 4) 2^28", n, 12,
+           lambda: lib.tb200_scan_by_key(p(keys), p(vals), p(vo), n, 4, 8, 0, 0, None, p(ws3), C.byref(need3), st),
+           cpu=cpu_time(lambda: ora.scan_by_key(hk, hv), cpu_n))
+    del ws3
+    ko4 = torch.empty_like(keys)
+    ws4, need4 = ws_for("tb200_unique_by_key_copy", None, None, None, None, n, 4, 4, None)
+    record("unique_by_key_copy int32/4-byte runs(mean 4) 2^28", n, 10,
+           lambda: lib.tb200_unique_by_key_copy(p(keys), p(vals), p(ko4), p(vo), n, 4, 4, p(cnt), p(ws4), C.byref(need4), st),
+           cpu=cpu_time(lambda: ora.unique_by_key_copy(hk, hv), cpu_n))
+    del ko4, ws4
+    idx2 = torch.zeros(2, dtype=torch.int64, device="cuda")
+    ws5, need5 = ws_for("tb200_minmax_element", None, n, 4, None)
+    record("minmax_element int32 2^28", n, 4, lambda: lib.tb200_minmax_element(p(keys), n, 4, p(idx2), p(ws5), C.byref(need5), st),
+           cpu=cpu_time(lambda: ora.minmax_element(hk), cpu_n))
+    del keys, vals, o1, o2, vo, ws5
     na = 1 << 27
     hma, hmb = dg.merge_keys_u64(cpu_n // 2, 4), dg.merge_keys_u64(cpu_n // 2, 5)
     hmva = np.arange(cpu_n // 2, dtype=np.uint32)

@@ -133,6 +133,18 @@ int tb200_unique_by_key_copy(const void* d_keys, const void* d_vals, void* d_key
                              unsigned long long* d_count, void* d_ws, size_t* ws_bytes,
                              tb200_stream_t stream);
 
+/* thrust::min_element / max_element / minmax_element(first, last) with thrust::less --
+ * thrust/system/cuda/detail/extrema.h:376-569 (the second of the "next" components).  The POSITION
+ * of the first smallest / first largest element is written to device memory: d_index[0] for
+ * min_element and max_element; d_index[0] = minimum and d_index[1] = maximum for minmax_element.
+ * n == 0 writes 0 (first == last).  t: any dtype.  NaNs compare false both ways, as with less. */
+int tb200_min_element(const void* d_in, size_t n, int t, unsigned long long* d_index, void* d_ws,
+                      size_t* ws_bytes, tb200_stream_t stream);
+int tb200_max_element(const void* d_in, size_t n, int t, unsigned long long* d_index, void* d_ws,
+                      size_t* ws_bytes, tb200_stream_t stream);
+int tb200_minmax_element(const void* d_in, size_t n, int t, unsigned long long* d_index,
+                         void* d_ws, size_t* ws_bytes, tb200_stream_t stream);
+
 /* thrust::merge / thrust::merge_by_key(A, B, [payload A, payload B,] out, [payload out,] comp)
  * with thrust::less (descending=0) or thrust::greater (descending=1) --
  * thrust/system/cuda/detail/merge.h:862-1013.  Both inputs must already be sorted by comp.

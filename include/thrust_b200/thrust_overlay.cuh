@@ -42,6 +42,7 @@
 #include <cstdint>
 #include <type_traits>
 
+#include "extrema.cuh"
 #include "merge.cuh"
 #include "radix_sort.cuh"
 #include "reduce.cuh"
@@ -545,6 +546,55 @@ OutIt merge(Policy& policy, KeysIt1 keys1_first, KeysIt1 keys1_last, KeysIt2 key
 template <class Policy, class KeysIt1, class KeysIt2, class OutIt, tb200_overlay::enable_for<Policy> = 0>
 OutIt merge(Policy& policy, KeysIt1 keys1_first, KeysIt1 keys1_last, KeysIt2 keys2_first, KeysIt2 keys2_last, OutIt result) {
   return cuda_cub::merge(policy, keys1_first, keys1_last, keys2_first, keys2_last, result, thrust::less<tb200_overlay::value_t<KeysIt1>>());
+}
+
+// ------------------------------------------------------------------------------------- extrema
+// replaces cuda_cub::min_element / max_element / minmax_element (thrust/system/cuda/detail/extrema.h:412-565)
+namespace tb200_overlay {
+template <class Policy, class It, class BinaryPred>
+thrust::pair<std::size_t, std::size_t> extrema_positions(Policy& policy, It first, std::size_t n, BinaryPred binary_pred) {
+  using T = value_t<It>;
+  scratch<Policy> tmp(policy, ::tb200::extrema_workspace_bytes<T>() + 256);
+  unsigned long long* d_index = reinterpret_cast<unsigned long long*>(tmp.at(up256(::tb200::extrema_workspace_bytes<T>())));
+  cudaError_t e = ::tb200::extrema_async(unwrap(first), n, T(), binary_pred, d_index, tmp.at(), cuda_cub::stream(policy));
+  cuda_cub::throw_on_error(e, "extrema: launch failed");
+  unsigned long long h[2];
+  cuda_cub::throw_on_error(cudaMemcpyAsync(h, d_index, sizeof(h), cudaMemcpyDeviceToHost, cuda_cub::stream(policy)), "extrema: read-back failed");
+  cuda_cub::throw_on_error(cudaStreamSynchronize(cuda_cub::stream(policy)), "extrema: synchronize failed");
+  return thrust::make_pair((std::size_t)h[0], (std::size_t)h[1]);
+}
+}  // namespace tb200_overlay
+
+template <class Policy, class ItemsIt, class BinaryPred, tb200_overlay::enable_for<Policy> = 0>
+ItemsIt min_element(Policy& policy, ItemsIt first, ItemsIt last, BinaryPred binary_pred) {
+  const std::size_t n = (std::size_t)thrust::distance(first, last);
+  if (n == 0) return last;
+  return first + tb200_overlay::extrema_positions(policy, first, n, binary_pred).first;
+}
+template <class Policy, class ItemsIt, tb200_overlay::enable_for<Policy> = 0>
+ItemsIt min_element(Policy& policy, ItemsIt first, ItemsIt last) {
+  return cuda_cub::min_element(policy, first, last, thrust::less<tb200_overlay::value_t<ItemsIt>>());
+}
+template <class Policy, class ItemsIt, class BinaryPred, tb200_overlay::enable_for<Policy> = 0>
+ItemsIt max_element(Policy& policy, ItemsIt first, ItemsIt last, BinaryPred binary_pred) {
+  const std::size_t n = (std::size_t)thrust::distance(first, last);
+  if (n == 0) return last;
+  return first + tb200_overlay::extrema_positions(policy, first, n, binary_pred).second;
+}
+template <class Policy, class ItemsIt, tb200_overlay::enable_for<Policy> = 0>
+ItemsIt max_element(Policy& policy, ItemsIt first, ItemsIt last) {
+  return cuda_cub::max_element(policy, first, last, thrust::less<tb200_overlay::value_t<ItemsIt>>());
+}
+template <class Policy, class ItemsIt, class BinaryPred, tb200_overlay::enable_for<Policy> = 0>
+thrust::pair<ItemsIt, ItemsIt> minmax_element(Policy& policy, ItemsIt first, ItemsIt last, BinaryPred binary_pred) {
+  const std::size_t n = (std::size_t)thrust::distance(first, last);
+  if (n == 0) return thrust::make_pair(last, last);
+  const thrust::pair<std::size_t, std::size_t> p = tb200_overlay::extrema_positions(policy, first, n, binary_pred);
+  return thrust::make_pair(first + p.first, first + p.second);
+}
+template <class Policy, class ItemsIt, tb200_overlay::enable_for<Policy> = 0>
+thrust::pair<ItemsIt, ItemsIt> minmax_element(Policy& policy, ItemsIt first, ItemsIt last) {
+  return cuda_cub::minmax_element(policy, first, last, thrust::less<tb200_overlay::value_t<ItemsIt>>());
 }
 
 }  // namespace cuda_cub

@@ -182,6 +182,15 @@ class Oracle:
         assert n >= 0
         return ko[:n].copy(), vo[:n].copy()
 
+    # -- extrema -------------------------------------------------------------------------------
+    def minmax_element(self, x):
+        """(position of the first smallest element, position of the first largest)."""
+        x = np.ascontiguousarray(x)
+        idx = np.zeros(2, dtype=np.uint64)
+        rc = self.lib.ora_minmax_element(_ptr(x), C.c_size_t(x.size), DTYPES[x.dtype], _ptr(idx))
+        assert rc == 0
+        return int(idx[0]), int(idx[1])
+
     # -- merge ---------------------------------------------------------------------------------
     def merge_by_key(self, ka, kb, va=None, vb=None, descending=False):
         ka = np.ascontiguousarray(ka)

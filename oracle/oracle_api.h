@@ -91,6 +91,11 @@ int ora_scan_by_key(const void* keys, const void* vals, void* out, size_t n, int
 int64_t ora_unique_by_key_copy(const void* keys, const void* vals, void* keys_out, void* vals_out,
                                size_t n, int key_t, int val_bytes);
 
+/* thrust::minmax_element(first, last) with less: idx[0] = position of the first smallest element,
+ * idx[1] = position of the first largest (thrust::min_element / max_element return the same two).
+ * n == 0 gives 0 and 0.  All ten dtypes. */
+int ora_minmax_element(const void* in, size_t n, int t, uint64_t* idx);
+
 /* thrust::merge / thrust::merge_by_key with less (or greater when descending=1); ties take
  * from range A first.  val_bytes in {0, 4, 8}. */
 int ora_merge_by_key(const void* ka, const void* va, size_t na, const void* kb, const void* vb,

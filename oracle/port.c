@@ -433,6 +433,23 @@ ORA_EXPORT int64_t ora_unique_by_key_copy(const void* keys, const void* vals, vo
   return cnt;
 }
 
+/* ---------------------------------------------------------------- extrema
+ * One sequential walk with strict comparisons, so the first smallest and the first largest element
+ * win (thrust/system/detail/sequential/extrema.h:36-118: "if comp(*first, *min) min = first" and
+ * "if comp(*max, *first) max = first"). */
+#define MINMAX_CASE(T, CODE)                                                           \
+  if (t == CODE) {                                                                     \
+    const T* p = (const T*)in; size_t lo = 0, hi = 0;                                  \
+    for (size_t i = 1; i < n; ++i) { if (p[i] < p[lo]) lo = i; if (p[hi] < p[i]) hi = i; } \
+    idx[0] = lo; idx[1] = hi; return 0;                                                \
+  }
+ORA_EXPORT int ora_minmax_element(const void* in, size_t n, int t, uint64_t* idx) {
+  MINMAX_CASE(int8_t, ORA_I8) MINMAX_CASE(uint8_t, ORA_U8) MINMAX_CASE(int16_t, ORA_I16) MINMAX_CASE(uint16_t, ORA_U16)
+  MINMAX_CASE(int32_t, ORA_I32) MINMAX_CASE(uint32_t, ORA_U32) MINMAX_CASE(int64_t, ORA_I64) MINMAX_CASE(uint64_t, ORA_U64)
+  MINMAX_CASE(float, ORA_F32) MINMAX_CASE(double, ORA_F64)
+  return -1;
+}
+
 /* ---------------------------------------------------------------- merge
  * Sequential two-finger merge; on equal keys the element of range A is emitted first
  * (thrust/system/detail/sequential/merge.inl:36-76 and :85-140: "if comp(*first2, *first1) take

@@ -14,6 +14,7 @@
 #include <thrust/partition.h>
 #include <thrust/unique.h>
 #include <thrust/merge.h>
+#include <thrust/extrema.h>
 #include <thrust/scan.h>
 #include <thrust/functional.h>
 #include <thrust/iterator/zip_iterator.h>
@@ -329,6 +330,20 @@ ORA_EXPORT int64_t ora_unique_by_key_copy(const void* keys, const void* vals, vo
     });
   });
   return cnt;
+}
+
+ORA_EXPORT int ora_minmax_element(const void* in, size_t n, int t, uint64_t* idx) {
+  return by_dtype(t, [&](auto tv) {
+    using T = decltype(tv);
+    const T* p = static_cast<const T*>(in);
+    // the three entry points are called separately: they must agree
+    auto both = thrust::minmax_element(thrust::device, p, p + n);
+    const T* lo = thrust::min_element(thrust::device, p, p + n);
+    const T* hi = thrust::max_element(thrust::device, p, p + n);
+    idx[0] = (uint64_t)(lo - p);
+    idx[1] = (uint64_t)(hi - p);
+    if (both.first != lo || both.second != hi) { idx[0] = ~(uint64_t)0; idx[1] = ~(uint64_t)0; }
+  });
 }
 
 ORA_EXPORT int ora_merge_by_key(const void* ka, const void* va, size_t na, const void* kb,

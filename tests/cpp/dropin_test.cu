@@ -16,6 +16,7 @@
 #include <thrust/merge.h>
 #include <thrust/partition.h>
 #include <thrust/reduce.h>
+#include <thrust/extrema.h>
 #include <thrust/scan.h>
 #include <thrust/sequence.h>
 #include <thrust/sort.h>
@@ -135,6 +136,16 @@ int main() {
     CHECK((ue.first - dkeys.begin()) == runs.back() + 1);
     got = dpos; ok = true; { int r = 0; for (int i = 0; i < n && ok; ++i) if (i == 0 || runs[i] != runs[i - 1]) { ok = got[r] == i; ++r; } } CHECK(ok); }
 
+  // extrema: first smallest / first largest (testing/minmax_element.cu:8-20)
+  { int raw[6] = {3, 5, 1, 2, 5, 1};
+    thrust::device_vector<int> dx(raw, raw + 6);
+    CHECK(thrust::min_element(thrust::device, dx.begin(), dx.end()) - dx.begin() == 2);
+    CHECK(thrust::max_element(thrust::device, dx.begin(), dx.end()) - dx.begin() == 1);
+    auto mm = thrust::minmax_element(thrust::device, dx.begin(), dx.end());
+    CHECK(mm.first - dx.begin() == 2 && mm.second - dx.begin() == 1);
+    auto big = thrust::max_element(thrust::device, d.begin(), d.end(), thrust::greater<int>());   // = the first minimum
+    CHECK(big - d.begin() == std::min_element(h.begin(), h.end()) - h.begin()); }
+
   // merge_by_key: ties take from the first range
   { int na = 300007, nb = 200003; std::vector<unsigned long long> a(na), b(nb); for (int i = 0; i < na; ++i) a[i] = mix(i) >> 52; for (int i = 0; i < nb; ++i) b[i] = mix(i + na) >> 52;
     std::sort(a.begin(), a.end()); std::sort(b.begin(), b.end());
@@ -152,7 +163,7 @@ int main() {
 
   // the overlay, not the stock CUB path, served these calls
   std::printf("overlay served %llu calls\n", thrust::cuda_cub::tb200_overlay::call_count());
-  CHECK(thrust::cuda_cub::tb200_overlay::call_count() == 24);
+  CHECK(thrust::cuda_cub::tb200_overlay::call_count() == 28);
   cudaStreamDestroy(s);
   if (cudaDeviceSynchronize() != cudaSuccess) { std::printf("FAILED: sticky CUDA error\n"); ++failures; }
   std::printf(failures ? "dropin_test: %d FAILURES\n" : "dropin_test: all checks passed\n", failures);

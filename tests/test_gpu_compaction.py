@@ -61,6 +61,32 @@ def test_copy_if_extremes_in_place_misaligned(tb, port):
     assert np.array_equal(host(tb.copy_if(misaligned(x, 3), "mod_eq", 2, 0)), port.copy_if(x, "mod_eq", 2, 0))
 
 
+@pytest.mark.parametrize("dt", [np.int32, np.int64])
+def test_compaction_large_bit_exact(tb, oracles, dt):
+    """2^25 + 12345 items (thousands of tiles, a partial last one), out of place and in place."""
+    n = (1 << 25) + 12345
+    x = dg.compaction_input(n).astype(dt)
+    keys = dg.run_keys(n).astype(dt)
+    stencil = (dg.scan_input_i32(n, 9) & 3).astype(np.int32)
+    got = host(tb.copy_if(dev(x), "mod_eq", 3, 1))
+    got_st = host(tb.copy_if(dev(x), "ne", 0, 0, stencil=dev(stencil)))
+    gt, gf = tb.partition_copy(dev(x), "lt", 1 << 20, 0)
+    d = dev(x)
+    split = tb.partition(d, "mod_eq", 2, 0)
+    u = host(tb.unique_copy(dev(keys)))
+    dk = dev(keys)
+    ui = host(tb.unique(dk))
+    for o in oracles:
+        assert np.array_equal(got, o.copy_if(x, "mod_eq", 3, 1))
+        assert np.array_equal(got_st, o.copy_if(x, "ne", 0, 0, stencil=stencil))
+        ot, of = o.partition_copy(x, "lt", 1 << 20, 0)
+        assert np.array_equal(host(gt), ot) and np.array_equal(host(gf), of)
+        sd, sc = o.stable_partition(x, "mod_eq", 2, 0)
+        assert split == sc and np.array_equal(host(d), sd)
+        ref_u = o.unique_copy(keys)
+        assert np.array_equal(u, ref_u) and np.array_equal(ui, ref_u)
+
+
 @pytest.mark.parametrize("n", EDGE_SIZES)
 def test_unique_and_reduce_by_key(tb, oracles, n):
     keys = dg.run_keys(n)

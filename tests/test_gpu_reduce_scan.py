@@ -53,6 +53,26 @@ def test_scan_int_bit_exact(tb, oracles, n):
         assert np.array_equal(excl, o.exclusive_scan(x, 5))
 
 
+@pytest.mark.parametrize("dt", [np.int32, np.int64, np.uint32, np.float64])
+def test_scan_chunked_route_bit_exact(tb, oracles, dt):
+    """Large inputs take the two-pass route (per-chunk totals, then chunk-wise scans); sizes chosen
+    so that the last chunk is short and the last tile partial.  float64 holds integers here, so its
+    sums are exact too."""
+    n = (1 << 25) + 12345
+    x = dg.scan_input_i32(n).astype(dt)
+    init = np.asarray(5, dtype=dt)[()]
+    incl = host(tb.inclusive_scan(dev(x)))
+    excl = host(tb.exclusive_scan(dev(x), init))
+    d = dev(x)
+    tb.inclusive_scan(d, out=d)                                                # in place
+    mx = host(tb.inclusive_scan(dev(x), op="max"))
+    for o in oracles:
+        assert np.array_equal(incl, o.inclusive_scan(x))
+        assert np.array_equal(excl, o.exclusive_scan(x, init))
+        assert np.array_equal(host(d), o.inclusive_scan(x))
+        assert np.array_equal(mx, o.inclusive_scan(x, "max"))
+
+
 def test_scan_in_place_and_misaligned(tb, port):
     x = dg.scan_input_i32(100001)
     d = dev(x)

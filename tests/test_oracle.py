@@ -217,3 +217,18 @@ def test_known_answers_by_key(oracles):
         assert o.scan_by_key(keys, ones, "plus", True, 5).tolist() == [5, 6, 7, 5, 6, 5, 5, 6, 7, 8]
         k, v = o.unique_by_key_copy(np.array([1, 3, 3, 3, 2, 2, 1], np.int32), np.array([9, 8, 7, 6, 5, 4, 3], np.uint32))
         assert k.tolist() == [1, 3, 2, 1] and v.tolist() == [9, 8, 5, 3]
+
+
+def test_extrema_known_answers_and_port_vs_ref(oracles, port, ref):
+    # testing/minmax_element.cu:8-20, testing/min_element.cu, testing/max_element.cu (the "Simple" cases)
+    data = np.array([3, 5, 1, 2, 5, 1], np.int32)
+    for o in oracles:
+        assert o.minmax_element(data) == (2, 1)
+        assert o.minmax_element(np.zeros(0, np.int32)) == (0, 0)
+        assert o.minmax_element(np.array([7], np.uint8)) == (0, 0)
+        assert o.minmax_element(np.full(1000, 4, np.int64)) == (0, 0)        # all equivalent: the first
+    rng = np.random.default_rng(11)
+    for dt in (np.int8, np.uint8, np.int16, np.uint16, np.int32, np.uint32, np.int64, np.uint64, np.float32, np.float64):
+        for n in (1, 2, 33, 1000, 100003):
+            x = rng.integers(0, 50, n).astype(dt) if n < 2000 else (rng.standard_normal(n) * 1000).astype(dt)
+            assert port.minmax_element(x) == ref.minmax_element(x), (dt, n)

@@ -28,6 +28,9 @@ PROTOTYPES = {
     "tb200_reduce_by_key": [_vp, _vp, _vp, _vp, _sz, _i, _i, _i, _vp, _vp, _szp, _vp],
     "tb200_scan_by_key": [_vp, _vp, _vp, _sz, _i, _i, _i, _i, _vp, _vp, _szp, _vp],
     "tb200_unique_by_key_copy": [_vp, _vp, _vp, _vp, _sz, _i, _i, _vp, _vp, _szp, _vp],
+    "tb200_min_element": [_vp, _sz, _i, _vp, _vp, _szp, _vp],
+    "tb200_max_element": [_vp, _sz, _i, _vp, _vp, _szp, _vp],
+    "tb200_minmax_element": [_vp, _sz, _i, _vp, _vp, _szp, _vp],
     "tb200_merge_by_key": [_vp, _vp, _sz, _vp, _vp, _sz, _vp, _vp, _i, _i, _i, _vp, _szp, _vp],
     "tb200_merge_sort_by_key": [_vp, _vp, _vp, _vp, _sz, _i, _i, _i, _vp, _szp, _vp],
     "tb200_merge_runs": [_vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _szp, _vp],

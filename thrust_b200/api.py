@@ -280,6 +280,31 @@ def unique_by_key(keys, vals):
     return unique_by_key_copy(keys, vals, keys, vals)
 
 
+# ------------------------------------------------------------------------------------- extrema
+def _extrema(fn, x, words):
+    _require_cuda(x)
+    idx = torch.zeros(words, dtype=torch.int64, device="cuda")
+    ws = _call_with_ws("reduce", fn, _ptr(x), x.numel(), DTYPE_CODE[x.dtype], _ptr(idx))
+    _sync_and_check(ws, fn)
+    return [int(v) for v in idx.cpu().tolist()]
+
+
+def min_element(x):
+    """thrust::min_element(first, last): position of the first smallest element (0 when empty)."""
+    return _extrema("tb200_min_element", x, 1)[0]
+
+
+def max_element(x):
+    """thrust::max_element(first, last): position of the first largest element (0 when empty)."""
+    return _extrema("tb200_max_element", x, 1)[0]
+
+
+def minmax_element(x):
+    """thrust::minmax_element(first, last): (position of the first smallest, of the first largest)."""
+    lo, hi = _extrema("tb200_minmax_element", x, 2)
+    return lo, hi
+
+
 # ------------------------------------------------------------------------------------- merge
 def merge_by_key(keys_a, keys_b, vals_a=None, vals_b=None, descending=False, sync=True):
     """thrust::merge_by_key(A, B, payload A, payload B, keys_out, payload_out[, greater]); with no
