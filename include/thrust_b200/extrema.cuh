@@ -1,7 +1,8 @@
 // min_element / max_element / minmax_element for sm_100a: one launch, every element read once.
 //
 // Each thread walks its share of the input with 16-byte streaming loads and keeps the smallest and
-// the largest value seen together with their positions; strict comparisons and increasing positions
+// the largest value seen together with their positions (a vector is inspected element by element
+// only when it holds a new extreme, which soon becomes rare); strict comparisons and increasing positions
 // inside a thread, and "equivalent values: the smaller position wins" wherever two candidates meet
 // (warp shuffles, CTA partials, the last CTA's fold of all partials), give the FIRST smallest and
 // the FIRST largest element, as the arg_min_f / arg_max_f functors of
@@ -61,8 +62,15 @@ extrema_kernel(InIt in, size_t n, Less less, extrema_state<T>* partials, unsigne
 #pragma unroll
       for (int u = 0; u < EXTREMA_UNROLL; ++u) {
         const T* e = reinterpret_cast<const T*>(&r[u]);
+        // the running extremes change rarely: look at a vector's elements one by one only when its
+        // own smallest or largest beats them (strict, so an equal later element never replaces)
+        T lo = e[0], hi = e[0];
 #pragma unroll
-        for (int k = 0; k < VEC; ++k) see(e[k], (v + u * stride) * VEC + k);
+        for (int k = 1; k < VEC; ++k) { if (less(e[k], lo)) lo = e[k]; if (less(hi, e[k])) hi = e[k]; }
+        if (!acc.has || less(lo, acc.v.min_v) || less(acc.v.max_v, hi)) {
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) see(e[k], (v + u * stride) * VEC + k);
+        }
       }
     }
     for (; v < nvec; v += stride) {

@@ -3,7 +3,7 @@
     python -m thrust_b200.profile_case <algorithm> <log2 n> [repetitions]
 
 algorithm: reduce | scan | sort | sort64 | copy_if | partition_copy | unique | reduce_by_key | merge |
-merge_sort.  Intended for captures such as
+merge_sort | scan_by_key | unique_by_key | minmax.  Intended for captures such as
     ncu --set full --clock-control none -k regex:<kernel> -s 1 -c 1 -o out python -m thrust_b200.profile_case scan 26
 on a case small enough for the profiler (a few hundred MB) yet larger than the 126 MB L2.
 """
@@ -43,6 +43,15 @@ def main():
     elif algo == "reduce_by_key":
         k, v = dev(dg.run_keys(n)), dev(dg.run_values_f32(n))
         run = lambda: tb.reduce_by_key(k, v)  # noqa: E731
+    elif algo == "scan_by_key":
+        k, v = dev(dg.run_keys(n)), dev(dg.run_values_f32(n))
+        run = lambda: tb.inclusive_scan_by_key(k, v)  # noqa: E731
+    elif algo == "unique_by_key":
+        k, v = dev(dg.run_keys(n)), dev(dg.run_values_f32(n))
+        run = lambda: tb.unique_by_key_copy(k, v)  # noqa: E731
+    elif algo == "minmax":
+        x = dev(dg.reduce_input(n))
+        run = lambda: tb.minmax_element(x)  # noqa: E731
     elif algo == "merge":
         a, b = dev(dg.merge_keys_u64(n, 4)), dev(dg.merge_keys_u64(n, 5))
         va = torch.arange(n, dtype=torch.int32, device="cuda")
