@@ -103,33 +103,67 @@ struct equal_op { template <class T> __host__ __device__ bool operator()(const T
 struct less_op { template <class T> __host__ __device__ bool operator()(const T& a, const T& b) const { return a < b; } };
 struct greater_op { template <class T> __host__ __device__ bool operator()(const T& a, const T& b) const { return b < a; } };
 
-// Predicate of the C ABI: kind 0: x % a == b, 1: x < a, 2: x >= a, 3: x != a.
-// make() picks cheaper forms of the modulo test where they give the same answer: a mask when a is
-// a power of two and b is 0 (true for negative x too in two's complement), 32-bit division when
-// the operands fit; the 64-bit division remains the general case.
+// Predicates of the C ABI.  kind 0: x % a == b, 1: x < a, 2: x >= a, 3: x != a; make() adds cheaper
+// forms of the modulo test where they give the same answer: kind 4, a mask, when a is a power of two
+// and b is 0 (true for negative x too in two's complement; kind 6 when the mask fits 31 bits),
+// kind 5, 32-bit division, when the operands fit; the 64-bit division remains the general case.
+//
+// abi_pred itself decides per element (a switch on `kind`: about 20 instructions per element, which
+// is what a streaming kernel can afford in total); visit() hands a caller the same predicate as a
+// type whose operator() is the one comparison, so that the hot kernels are compiled per kind.
+struct pred_mod64 { long long a, b; template <class T> __host__ __device__ bool operator()(const T& x) const { return (long long)x % a == b; } };
+struct pred_lt { long long a; template <class T> __host__ __device__ bool operator()(const T& x) const { return x < (T)a; } };
+struct pred_ge { long long a; template <class T> __host__ __device__ bool operator()(const T& x) const { return x >= (T)a; } };
+struct pred_ne { long long a; template <class T> __host__ __device__ bool operator()(const T& x) const { return x != (T)a; } };
+struct pred_mask { long long a; template <class T> __host__ __device__ bool operator()(const T& x) const { return ((long long)x & a) == 0; } };
+struct pred_mask32 {   // the mask fits 31 bits: only the low word of x matters
+  long long a;
+  template <class T> __host__ __device__ bool operator()(const T& x) const {
+    if (std::is_integral<T>::value) return ((unsigned)x & (unsigned)a) == 0;
+    return ((long long)x & a) == 0;
+  }
+};
+struct pred_mod32 {
+  long long a, b;
+  template <class T> __host__ __device__ bool operator()(const T& x) const {
+    if (sizeof(T) <= 4 && std::is_integral<T>::value) {
+      if (std::is_signed<T>::value) return (int)x % (int)a == (int)b;
+      return (unsigned)x % (unsigned)a == (unsigned)b;
+    }
+    return (long long)x % a == b;
+  }
+};
 struct abi_pred {
   int kind; long long a, b;
   static abi_pred make(int kind, long long a, long long b) {
     abi_pred p; p.kind = kind; p.a = a; p.b = b;
     if (kind == 0) {
-      if (b == 0 && a > 0 && (a & (a - 1)) == 0) { p.kind = 4; p.a = a - 1; }
+      if (b == 0 && a > 0 && (a & (a - 1)) == 0) { p.kind = a - 1 <= 0x7fffffffll ? 6 : 4; p.a = a - 1; }
       else if (a > 0 && a <= 0x7fffffffll && b >= 0 && b <= 0x7fffffffll) p.kind = 5;
     }
     return p;
   }
   template <class T> __host__ __device__ bool operator()(const T& x) const {
     switch (kind) {
-      case 0: return (long long)x % a == b;
-      case 1: return x < (T)a;
-      case 2: return x >= (T)a;
-      case 3: return x != (T)a;
-      case 4: return ((long long)x & a) == 0;
-      default:
-        if (sizeof(T) <= 4 && std::is_integral<T>::value) {
-          if (std::is_signed<T>::value) return (int)x % (int)a == (int)b;
-          return (unsigned)x % (unsigned)a == (unsigned)b;
-        }
-        return (long long)x % a == b;
+      case 0: return pred_mod64{a, b}(x);
+      case 1: return pred_lt{a}(x);
+      case 2: return pred_ge{a}(x);
+      case 3: return pred_ne{a}(x);
+      case 4: return pred_mask{a}(x);
+      case 6: return pred_mask32{a}(x);
+      default: return pred_mod32{a, b}(x);
+    }
+  }
+  // f(typed predicate): host side
+  template <class F> auto visit(F f) const -> decltype(f(pred_lt{0})) {
+    switch (kind) {
+      case 0: return f(pred_mod64{a, b});
+      case 1: return f(pred_lt{a});
+      case 2: return f(pred_ge{a});
+      case 3: return f(pred_ne{a});
+      case 4: return f(pred_mask{a});
+      case 6: return f(pred_mask32{a});
+      default: return f(pred_mod32{a, b});
     }
   }
 };

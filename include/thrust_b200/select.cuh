@@ -1,6 +1,9 @@
-// Single-pass stream compaction for sm_100a: copy_if (with or without a stencil), partition,
-// partition_copy and unique / unique_copy share one kernel.
+// Stream compaction for sm_100a: copy_if (with or without a stencil), partition, partition_copy and
+// unique / unique_copy.  This file holds the single-pass kernel that serves every case (any iterator,
+// stencils, in-place forms, small and medium inputs) and the dispatch; large contiguous inputs whose
+// outputs do not overlap them go to the two-pass streaming kernels of select_stream.cuh.
 //
+// Single pass:
 // One CTA per tile (dynamic ticket).  A tile loads its items with the same lane-interleaved
 // 16-byte pattern as the scan, evaluates a keep/drop flag per item, runs the tile-wide exclusive
 // prefix (warp shuffles + decoupled look-back over preceding tiles) on the per-vector keep counts,
@@ -16,6 +19,7 @@
 // restores input order; so partition here is always the stable one.
 #pragma once
 #include "common.cuh"
+#include "select_stream.cuh"
 
 namespace tb200 {
 
@@ -161,19 +165,40 @@ partition_finish_kernel(T* data, const T* scratch, size_t n, const ws_header* hd
 template <class T> constexpr size_t select_tile_items() { return (size_t)SELECT_BLOCK * select_tuning<T>::IPT; }
 template <class T> size_t select_workspace_bytes(size_t n) {
   size_t tiles = (n + select_tile_items<T>() - 1) / select_tile_items<T>();
-  return sizeof(ws_header) + tile_state<unsigned long long>::bytes(tiles + 1);   // large enough for either offset width
+  const size_t single = sizeof(ws_header) + tile_state<unsigned long long>::bytes(tiles + 1);   // large enough for either offset width
+  const size_t stream = select_stream_workspace_bytes<T>(n);
+  return single > stream ? single : stream;
 }
 
 // Launches the compaction; no sync.  The number of kept items goes to the workspace header and,
 // if d_count != nullptr, to *d_count.
-template <int MODE, bool KEEP_REJECTS, class InIt, class StIt, class SelIt, class RejIt, class T, class Pred>
+// ALLOW_STREAM = false keeps a caller that has already tried select_stream_async itself from
+// instantiating those kernels a second time.
+template <int MODE, bool KEEP_REJECTS, bool ALLOW_STREAM = true, class InIt, class StIt, class SelIt, class RejIt, class T, class Pred>
 cudaError_t select_async(InIt in, StIt stencil, SelIt out_sel, RejIt out_rej, size_t n, T /*type tag*/, Pred pred, bool mirrored,
                          unsigned long long* d_count, void* ws, cudaStream_t stream) {
   char* base = static_cast<char*>(ws);
   ws_header* hdr = reinterpret_cast<ws_header*>(base);
   constexpr int IPT = select_tuning<T>::IPT;
   const size_t tiles = (n + select_tile_items<T>() - 1) / select_tile_items<T>();
-  cudaError_t e = cudaMemsetAsync(base, 0, select_workspace_bytes<T>(n), stream);
+  // large contiguous inputs whose outputs are plain arrays that do not overlap the input: the
+  // two-pass streaming kernels (select_stream.cuh)
+  if constexpr (ALLOW_STREAM && MODE != SEL_STENCIL && std::is_pointer<InIt>::value && std::is_pointer<SelIt>::value && std::is_arithmetic<T>::value &&
+                (sizeof(T) == 4 || sizeof(T) == 8) && (!KEEP_REJECTS || std::is_pointer<RejIt>::value)) {
+    using In = typename std::remove_cv<typename std::remove_pointer<InIt>::type>::type;
+    using Sel = typename std::remove_pointer<SelIt>::type;
+    if constexpr (std::is_same<In, T>::value && std::is_same<Sel, T>::value) {
+      bool ok = true;
+      T* rej = nullptr;
+      if constexpr (KEEP_REJECTS) {
+        using Rej = typename std::remove_pointer<RejIt>::type;
+        if constexpr (std::is_same<Rej, T>::value) rej = out_rej; else ok = false;
+      }
+      if (ok && select_stream_eligible(in, out_sel, rej, KEEP_REJECTS && !mirrored, n, sizeof(T)))
+        return select_stream_async<MODE == SEL_UNIQUE, KEEP_REJECTS, T, Pred>(in, out_sel, rej, n, pred, mirrored, d_count, ws, stream);
+    }
+  }
+  cudaError_t e = cudaMemsetAsync(base, 0, sizeof(ws_header) + tile_state<unsigned long long>::bytes(tiles + 1), stream);
   if (e != cudaSuccess) return e;
   if (n == 0) { if (d_count) return cudaMemsetAsync(d_count, 0, sizeof(unsigned long long), stream); return cudaSuccess; }
   auto launch = [&](auto off_tag, auto vec_tag) {
@@ -200,16 +225,29 @@ cudaError_t select_async(InIt in, StIt stencil, SelIt out_sel, RejIt out_rej, si
   return cudaGetLastError();
 }
 
-// In-place stable partition of data[0, n): `scratch` holds n items.
-template <class T, class Pred>
-cudaError_t partition_inplace_async(T* data, T* scratch, size_t n, Pred pred, unsigned long long* d_count, void* ws, cudaStream_t stream) {
-  cudaError_t e = select_async<SEL_PRED, true>((const T*)data, (const T*)nullptr, scratch, (T*)nullptr, n, T(), pred, true, d_count, ws, stream);
-  if (e != cudaSuccess || n == 0) return e;
+template <class T>
+cudaError_t partition_finish_async(T* data, const T* scratch, size_t n, const void* ws, cudaStream_t stream) {
   const device_info& di = current_device_info();
   size_t grid = (n + 256 * 8 - 1) / (256 * 8);
   if (grid > (size_t)di.sm_count * 8) grid = (size_t)di.sm_count * 8;
   partition_finish_kernel<T><<<(unsigned)grid, 256, 0, stream>>>(data, scratch, n, reinterpret_cast<const ws_header*>(ws));
   return cudaGetLastError();
+}
+
+// In-place stable partition of data[0, n): `scratch` holds n items.
+template <bool ALLOW_STREAM = true, class T, class Pred>
+cudaError_t partition_inplace_async(T* data, T* scratch, size_t n, Pred pred, unsigned long long* d_count, void* ws, cudaStream_t stream) {
+  cudaError_t e = select_async<SEL_PRED, true, ALLOW_STREAM>((const T*)data, (const T*)nullptr, scratch, (T*)nullptr, n, T(), pred, true, d_count, ws, stream);
+  if (e != cudaSuccess || n == 0) return e;
+  return partition_finish_async(data, scratch, n, ws, stream);
+}
+
+// The same through the streaming kernels only (the caller has checked select_stream_eligible()).
+template <class T, class Pred>
+cudaError_t partition_inplace_stream_async(T* data, T* scratch, size_t n, Pred pred, unsigned long long* d_count, void* ws, cudaStream_t stream) {
+  cudaError_t e = select_stream_async<false, true, T, Pred>((const T*)data, scratch, (T*)nullptr, n, pred, true, d_count, ws, stream);
+  if (e != cudaSuccess) return e;
+  return partition_finish_async(data, scratch, n, ws, stream);
 }
 
 }  // namespace tb200

@@ -17,7 +17,12 @@ TB200_API int tb200_partition(void* d_data, size_t n, int t, int pred, long long
     if (n && !d_data) return ERR_INVALID;
     T* scratch = reinterpret_cast<T*>(static_cast<char*>(d_ws) + sel);
     abi_pred p = abi_pred::make(pred, a, b);
-    return (int)tb200::partition_inplace_async(static_cast<T*>(d_data), scratch, n, p, d_count, d_ws, stream);
+    // large inputs: the streaming kernels, compiled per predicate kind
+    if constexpr (sizeof(T) == 4 || sizeof(T) == 8) {
+      if (tb200::select_stream_eligible(d_data, scratch, nullptr, false, n, sizeof(T)))
+        return p.visit([&](auto typed) { return (int)tb200::partition_inplace_stream_async(static_cast<T*>(d_data), scratch, n, typed, d_count, d_ws, stream); });
+    }
+    return (int)tb200::partition_inplace_async<false>(static_cast<T*>(d_data), scratch, n, p, d_count, d_ws, stream);
   });
 }
 

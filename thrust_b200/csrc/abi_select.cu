@@ -13,8 +13,16 @@ int select_pred(const void* in, const void* stencil, int stencil_t, void* out_se
   const T* i = static_cast<const T*>(in);
   T* os = static_cast<T*>(out_sel);
   T* orj = static_cast<T*>(out_rej);
-  if (!stencil)
-    return (int)tb200::select_async<tb200::SEL_PRED, REJ>(i, (const T*)nullptr, os, orj, n, T(), pred, false, d_count, d_ws, stream);
+  if (!stencil) {
+    // large inputs: the streaming kernels, compiled per predicate kind
+    if constexpr (sizeof(T) == 4 || sizeof(T) == 8) {
+      if (tb200::select_stream_eligible(in, out_sel, out_rej, REJ, n, sizeof(T)))
+        return pred.visit([&](auto typed) {
+          return (int)tb200::select_stream_async<false, REJ, T, decltype(typed)>(i, os, orj, n, typed, false, d_count, d_ws, stream);
+        });
+    }
+    return (int)tb200::select_async<tb200::SEL_PRED, REJ, false>(i, (const T*)nullptr, os, orj, n, T(), pred, false, d_count, d_ws, stream);
+  }
   if (stencil_t == TB200_U8)
     return (int)tb200::select_async<tb200::SEL_STENCIL, REJ>(i, static_cast<const uint8_t*>(stencil), os, orj, n, T(), pred, false, d_count, d_ws, stream);
   if (stencil_t == TB200_I32)
