@@ -1,8 +1,7 @@
 // min_element / max_element / minmax_element for sm_100a: one launch, every element read once.
 //
 // Each thread walks its share of the input with 16-byte streaming loads and keeps the smallest and
-// the largest value seen together with their positions (a vector is inspected element by element
-// only when it holds a new extreme, which soon becomes rare); strict comparisons and increasing positions
+// the largest value seen together with their positions; strict comparisons and increasing positions
 // inside a thread, and "equivalent values: the smaller position wins" wherever two candidates meet
 // (warp shuffles, CTA partials, the last CTA's fold of all partials), give the FIRST smallest and
 // the FIRST largest element, as the arg_min_f / arg_max_f functors of
@@ -52,32 +51,42 @@ extrema_kernel(InIt in, size_t n, Less less, extrema_state<T>* partials, unsigne
     }
   };
   if constexpr (VEC > 0) {
+    // Per 16-byte vector only its smallest and largest value are compared with the running
+    // extremes, and only the VECTOR's position is recorded (strict comparisons: the earliest
+    // vector holding the extreme wins); the element inside the two winning vectors is found at
+    // the end by reading them once more.
     const size_t nvec = n / VEC;
     const vec16* vin = reinterpret_cast<const vec16*>(in);
+    T lo_v = T(), hi_v = T();
+    size_t lo_at = 0, hi_at = 0;
+    bool any = false;
+    auto see_vector = [&](const vec16& r, size_t at) {
+      const T* e = reinterpret_cast<const T*>(&r);
+      T lo = e[0], hi = e[0];
+#pragma unroll
+      for (int k = 1; k < VEC; ++k) { if (less(e[k], lo)) lo = e[k]; if (less(hi, e[k])) hi = e[k]; }
+      if (!any || less(lo, lo_v)) { lo_v = lo; lo_at = at; }
+      if (!any || less(hi_v, hi)) { hi_v = hi; hi_at = at; }
+      any = true;
+    };
     size_t v = tid;
     for (; v + (EXTREMA_UNROLL - 1) * stride < nvec; v += EXTREMA_UNROLL * stride) {
       vec16 r[EXTREMA_UNROLL];
 #pragma unroll
       for (int u = 0; u < EXTREMA_UNROLL; ++u) r[u] = load_stream16(vin + v + u * stride);
 #pragma unroll
-      for (int u = 0; u < EXTREMA_UNROLL; ++u) {
-        const T* e = reinterpret_cast<const T*>(&r[u]);
-        // the running extremes change rarely: look at a vector's elements one by one only when its
-        // own smallest or largest beats them (strict, so an equal later element never replaces)
-        T lo = e[0], hi = e[0];
-#pragma unroll
-        for (int k = 1; k < VEC; ++k) { if (less(e[k], lo)) lo = e[k]; if (less(hi, e[k])) hi = e[k]; }
-        if (!acc.has || less(lo, acc.v.min_v) || less(acc.v.max_v, hi)) {
-#pragma unroll
-          for (int k = 0; k < VEC; ++k) see(e[k], (v + u * stride) * VEC + k);
-        }
-      }
+      for (int u = 0; u < EXTREMA_UNROLL; ++u) see_vector(r[u], v + u * stride);
     }
-    for (; v < nvec; v += stride) {
-      vec16 r = load_stream16(vin + v);
-      const T* e = reinterpret_cast<const T*>(&r);
-#pragma unroll
-      for (int k = 0; k < VEC; ++k) see(e[k], v * VEC + k);
+    for (; v < nvec; v += stride) see_vector(load_stream16(vin + v), v);
+    if (any) {
+      const T* e = in + lo_at * VEC;
+      int k = 0;
+      while (k < VEC - 1 && (less(lo_v, e[k]) || less(e[k], lo_v))) ++k;     // first element equivalent to the minimum
+      see(e[k], lo_at * VEC + k);
+      e = in + hi_at * VEC;
+      k = 0;
+      while (k < VEC - 1 && (less(hi_v, e[k]) || less(e[k], hi_v))) ++k;
+      see(e[k], hi_at * VEC + k);
     }
     const size_t t = nvec * VEC + tid;
     if (t < n) see(in[t], t);
