@@ -458,7 +458,7 @@ def run_ours(args):
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u32", "data": "synthetic",
         "config": {"workload": WORKLOAD, "n": N_KEYS, "per_gpu": n_local,
                    "l2": "2 GiB of input per step (> 126 MB L2); the pristine input is restored by a 2 GiB device copy between timed steps",
-                   "parallelism": "1 GPU" if world == 1 else "%d GPUs: local radix sort + sampled splitters + merges that read the peers' shards over NVLink (CUDA IPC)" % world},
+                   "parallelism": "1 GPU" if world == 1 else "%d GPUs: sampled splitters, one scatter kernel per GPU storing each pair into the owning GPU's receive buffer over NVLink (CUDA IPC), local radix sort of what arrived" % world},
         "roofline": roofline, "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
         "wall_s_timed_region": t_wall,
         "sort_roofline": {"algorithmic_bytes_per_key": 68, "achieved_gbs": 68.0 * N_KEYS / ms / 1e6, "frac_of_hbm_peak": 68.0 * N_KEYS / ms / 1e6 / peak / world},

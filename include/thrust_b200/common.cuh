@@ -214,6 +214,18 @@ template <class T, class Op> __device__ __forceinline__ T warp_inclusive_scan(T 
   return x;
 }
 
+// The same where a lane may hold nothing (`has` false): such a lane ends up with what precedes it.
+template <class T, class Op> __device__ __forceinline__ T warp_inclusive_scan_if(T x, bool has, Op op) {
+  const int lane = lane_id();
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    T y = shfl_up(x, d);
+    const bool yh = __shfl_up_sync(FULL_MASK, (int)has, d) != 0;
+    if (lane >= d && yh) { x = has ? op(y, x) : y; has = true; }
+  }
+  return x;
+}
+
 // Reduction across a warp of values that may be absent; operands keep lane order (lower lane on
 // the left), so the operator need not commute.  Result valid in lane 0.
 template <class T, class Op> __device__ __forceinline__ opt<T> warp_reduce_opt(opt<T> x, Op op) {

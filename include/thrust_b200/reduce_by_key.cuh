@@ -15,6 +15,7 @@
 // thrust/system/cuda/detail/reduce_by_key.h:197-860.
 #pragma once
 #include "common.cuh"
+#include "reduce_by_key_stream.cuh"
 
 namespace tb200 {
 
@@ -160,7 +161,12 @@ reduce_by_key_kernel(KeyIt keys, ValIt vals, KeyOutIt keys_out, ValOutIt vals_ou
 template <class K, class V> constexpr size_t rbk_tile_items() { return (size_t)RBK_BLOCK * rbk_tuning<K, V>::IPT; }
 template <class K, class V> size_t rbk_workspace_bytes(size_t n) {
   size_t tiles = (n + rbk_tile_items<K, V>() - 1) / rbk_tile_items<K, V>();
-  return sizeof(ws_header) + tile_state<rbk_pair<unsigned long long, V>>::bytes(tiles + 1);
+  const size_t single = sizeof(ws_header) + tile_state<rbk_pair<unsigned long long, V>>::bytes(tiles + 1);
+  if constexpr (sizeof(K) == sizeof(V) && (sizeof(K) == 4 || sizeof(K) == 8)) {
+    const size_t stream = rbk_stream_workspace_bytes<K, V>(n);
+    return single > stream ? single : stream;
+  }
+  return single;
 }
 
 // Launches reduce_by_key; no sync.  The number of runs goes to the workspace header and, if
@@ -172,7 +178,20 @@ cudaError_t reduce_by_key_async(KeyIt keys, ValIt vals, KeyOutIt keys_out, ValOu
   ws_header* hdr = reinterpret_cast<ws_header*>(base);
   constexpr int IPT = rbk_tuning<K, V>::IPT;
   const size_t tiles = (n + rbk_tile_items<K, V>() - 1) / rbk_tile_items<K, V>();
-  cudaError_t e = cudaMemsetAsync(base, 0, rbk_workspace_bytes<K, V>(n), stream);
+  // large contiguous inputs with keys and values of one size and outputs elsewhere: the two-pass
+  // streaming kernels (reduce_by_key_stream.cuh)
+  if constexpr (std::is_pointer<KeyIt>::value && std::is_pointer<ValIt>::value && std::is_pointer<KeyOutIt>::value && std::is_pointer<ValOutIt>::value &&
+                sizeof(K) == sizeof(V) && (sizeof(K) == 4 || sizeof(K) == 8) && std::is_trivially_copyable<K>::value && std::is_trivially_copyable<V>::value) {
+    using KIn = typename std::remove_cv<typename std::remove_pointer<KeyIt>::type>::type;
+    using VIn = typename std::remove_cv<typename std::remove_pointer<ValIt>::type>::type;
+    using KOut = typename std::remove_pointer<KeyOutIt>::type;
+    using VOut = typename std::remove_pointer<ValOutIt>::type;
+    if constexpr (std::is_same<KIn, K>::value && std::is_same<VIn, V>::value && std::is_same<KOut, K>::value && std::is_same<VOut, V>::value) {
+      if (rbk_stream_eligible(keys, vals, keys_out, vals_out, n, sizeof(K)))
+        return reduce_by_key_stream_async<K, V, Eq, Op>(keys, vals, keys_out, vals_out, n, eq, op, d_count, ws, stream);
+    }
+  }
+  cudaError_t e = cudaMemsetAsync(base, 0, sizeof(ws_header) + tile_state<rbk_pair<unsigned long long, V>>::bytes(tiles + 1), stream);
   if (e != cudaSuccess) return e;
   if (n == 0) { if (d_count) return cudaMemsetAsync(d_count, 0, sizeof(unsigned long long), stream); return cudaSuccess; }
   const bool small = n < (1ull << 31);

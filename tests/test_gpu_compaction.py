@@ -87,6 +87,32 @@ def test_compaction_large_bit_exact(tb, oracles, dt):
         assert np.array_equal(u, ref_u) and np.array_equal(ui, ref_u)
 
 
+@pytest.mark.parametrize("kt,vt", [(np.int32, np.int32), (np.uint32, np.float32), (np.int64, np.int64), (np.uint64, np.float64), (np.int32, np.int64)])
+def test_reduce_by_key_large_bit_exact(tb, oracles, kt, vt):
+    """2^25 + 12345 items: keys and values of one size take the two-pass streaming kernels, mixed
+    sizes the single-pass one; the last row of the input is partial.  Integer sums, minima and the
+    first-of-run selection of unique_by_key are exact; floating-point values are small integers here,
+    so their sums are exact too."""
+    n = (1 << 25) + 12345
+    keys = dg.run_keys(n).astype(kt)
+    vals = (dg.scan_input_i32(n, 7) % 1000).astype(vt)
+    ko, vo = tb.reduce_by_key(dev(keys), dev(vals))
+    km, vm = tb.reduce_by_key(dev(keys), dev(vals), op="min")
+    uk, uv = (None, None)
+    if np.dtype(vt).itemsize in (4, 8):
+        uk, uv = tb.unique_by_key_copy(dev(keys), dev(vals))
+    dk, dv = dev(keys), dev(vals)
+    ik, iv = tb.unique_by_key(dk, dv)                                          # in place: single-pass kernel
+    for o in oracles:
+        rk, rv = o.reduce_by_key(keys, vals)
+        assert np.array_equal(host(ko), rk) and np.array_equal(host(vo), rv)
+        mk, mv = o.reduce_by_key(keys, vals, "min")
+        assert np.array_equal(host(km), mk) and np.array_equal(host(vm), mv)
+        fk, fv = o.unique_by_key_copy(keys, vals)
+        assert np.array_equal(host(uk), fk) and np.array_equal(host(uv), fv)
+        assert np.array_equal(host(ik), fk) and np.array_equal(host(iv), fv)
+
+
 @pytest.mark.parametrize("n", EDGE_SIZES)
 def test_unique_and_reduce_by_key(tb, oracles, n):
     keys = dg.run_keys(n)
