@@ -269,4 +269,111 @@ cudaError_t reduce_by_key_stream_async(const K* keys, const V* vals, K* keys_out
   return cudaGetLastError();
 }
 
+// ------------------------------------------------------------------------------------------------
+// inclusive / exclusive scan_by_key on the same plan: the batches' pairs and their scan are those of
+// reduce_by_key; the second pass writes, for every item, the reduction of its run so far (16-byte
+// stores at the items' own positions: nothing is compacted).  out may be vals exactly (in place).
+// Replaces the ScanByKeyAgent of thrust/system/cuda/detail/scan_by_key.h:172-588 for such inputs.
+template <bool INCLUSIVE, class K, class V, class Eq, class Op, int VEC>
+__global__ void __launch_bounds__(RBK_STREAM_BLOCK, RBK_STREAM_CTAS_PER_SM)
+scan_by_key_stream_kernel(const K* keys, const V* vals, V* out, size_t n, size_t rows, size_t batches, V init, Eq eq, Op op,
+                          const rbk_stream_pair<V>* batch_incl, ws_header* hdr, const ws_header* scan_hdr) {
+  using P = rbk_stream_pair<V>;
+  const rbk_stream_combine<V, Op> comb{op};
+  const int lane = lane_id();
+  const size_t gwarp = ((size_t)blockIdx.x * RBK_STREAM_BLOCK + threadIdx.x) >> 5;
+  const size_t nwarps = ((size_t)gridDim.x * RBK_STREAM_BLOCK) >> 5;
+  for (size_t batch = gwarp; batch < batches; batch += nwarps) {
+    const size_t first = batch * RBK_STREAM_ROWS;
+    P carry; carry.count = 0; carry.value = V();
+    if (batch > 0) carry = batch_incl[batch - 1];
+    K prev_tail = K(); bool have_prev = false;
+    select_batch_start(keys, first, VEC, prev_tail, have_prev);
+    K k[RBK_STREAM_ROWS][VEC];
+    V v[RBK_STREAM_ROWS][VEC];
+#pragma unroll
+    for (int u = 0; u < RBK_STREAM_ROWS; ++u)
+      if (first + u < rows) { select_row_load<K, VEC>(keys, n, first + u, lane, k[u]); select_row_load<V, VEC>(vals, n, first + u, lane, v[u]); }
+#pragma unroll
+    for (int u = 0; u < RBK_STREAM_ROWS; ++u) {
+      if (first + u >= rows) break;
+      const size_t row = first + u;
+      const bool row_full = (row + 1) * 32 * VEC <= n;
+      unsigned bits, valid;
+      P mine = rbk_stream_row<K, V, Eq, Op, VEC>(keys, vals, n, row, lane, eq, op, k[u], v[u], prev_tail, have_prev, bits, valid);
+      const rbk_stream_row_info<V> info = rbk_stream_row_scan<V, Op>(mine, row_full, valid != 0, lane, op);
+      P row_pair; row_pair.count = info.row_heads; row_pair.value = info.row_open;
+      // reduction of the run's items ahead of this lane's first item (meaningless if that item is a head)
+      V prev = !info.from_row_start ? info.carry_in : (lane == 0 ? carry.value : op(carry.value, info.carry_in));
+      V y[VEC];
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) {
+        if ((bits >> j) & 1) {
+          y[j] = INCLUSIVE ? v[u][j] : init;
+          prev = v[u][j];
+        } else {
+          const V cur = op(prev, v[u][j]);
+          y[j] = INCLUSIVE ? cur : op(init, prev);
+          prev = cur;
+        }
+      }
+      const size_t i0 = (row * 32 + lane) * VEC;
+      if (row_full) {
+        vec16 r;
+        V* e = reinterpret_cast<V*>(&r);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) e[j] = y[j];
+        store_stream16(reinterpret_cast<char*>(out) + i0 * sizeof(V), r);
+      } else {
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) if (i0 + j < n) out[i0 + j] = y[j];
+      }
+      carry = comb(carry, row_pair);
+    }
+    if (batch == batches - 1 && lane == 0) hdr->error = scan_hdr->error;
+  }
+}
+
+// Whether the streaming kernels may serve a scan_by_key: large, 16-byte aligned arrays; out is vals
+// itself or overlaps neither input.
+inline bool scan_by_key_stream_eligible(const void* keys, const void* vals, const void* out, size_t n, size_t item_bytes) {
+  if (n < RBK_STREAM_MIN_ITEMS) return false;
+  if (((reinterpret_cast<uintptr_t>(keys) | reinterpret_cast<uintptr_t>(vals) | reinterpret_cast<uintptr_t>(out)) & 15) != 0) return false;
+  const size_t bytes = n * item_bytes;
+  const char* kb = static_cast<const char*>(keys);
+  const char* vb = static_cast<const char*>(vals);
+  const char* ob = static_cast<const char*>(out);
+  if (ob < kb + bytes && kb < ob + bytes) return false;
+  if (ob != vb && ob < vb + bytes && vb < ob + bytes) return false;
+  return true;
+}
+
+// The caller has checked scan_by_key_stream_eligible() and sizeof(K) == sizeof(V) in {4, 8}.
+template <bool INCLUSIVE, class K, class V, class Eq, class Op>
+cudaError_t scan_by_key_stream_async(const K* keys, const V* vals, V* out, size_t n, V init, Eq eq, Op op, void* ws, cudaStream_t stream) {
+  static_assert(sizeof(K) == sizeof(V) && (sizeof(K) == 4 || sizeof(K) == 8), "keys and values of the same size, 4 or 8 bytes");
+  constexpr int VEC = 16 / sizeof(K);
+  using P = rbk_stream_pair<V>;
+  char* base = static_cast<char*>(ws);
+  ws_header* hdr = reinterpret_cast<ws_header*>(base);
+  const size_t rows = (n + 32 * VEC - 1) / (32 * VEC);
+  const size_t batches = rbk_stream_batches<K>(n);
+  const size_t arr = align_up(batches * sizeof(P), 256);
+  P* pairs = reinterpret_cast<P*>(base + sizeof(ws_header));
+  P* incl = reinterpret_cast<P*>(base + sizeof(ws_header) + arr);
+  void* scan_ws = base + sizeof(ws_header) + 2 * arr;
+  size_t ctas = (size_t)current_device_info().sm_count * RBK_STREAM_CTAS_PER_SM;
+  const size_t want = (batches + RBK_STREAM_BLOCK / 32 - 1) / (RBK_STREAM_BLOCK / 32);
+  if (ctas > want) ctas = want;
+  cudaError_t e = cudaMemsetAsync(hdr, 0, sizeof(ws_header), stream);
+  if (e != cudaSuccess) return e;
+  rbk_stream_count_kernel<K, V, Eq, Op, VEC><<<(unsigned)ctas, RBK_STREAM_BLOCK, 0, stream>>>(keys, vals, n, rows, batches, eq, op, pairs);
+  P none; none.count = 0; none.value = V();
+  e = scan_async<true>((const P*)pairs, incl, batches, none, false, rbk_stream_combine<V, Op>{op}, scan_ws, stream);
+  if (e != cudaSuccess) return e;
+  scan_by_key_stream_kernel<INCLUSIVE, K, V, Eq, Op, VEC><<<(unsigned)ctas, RBK_STREAM_BLOCK, 0, stream>>>(keys, vals, out, n, rows, batches, init, eq, op, incl, hdr,
+                                                                                                          static_cast<const ws_header*>(scan_ws));
+  return cudaGetLastError();
+}
+
 }  // namespace tb200

@@ -114,7 +114,12 @@ scan_by_key_kernel(KeyIt keys, ValIt vals, OutIt out, size_t n, V init, Eq key_e
 
 template <class K, class V> size_t scan_by_key_workspace_bytes(size_t n) {
   size_t tiles = (n + rbk_tile_items<K, V>() - 1) / rbk_tile_items<K, V>();
-  return sizeof(ws_header) + tile_state<rbk_pair<unsigned, V>>::bytes(tiles + 1);
+  const size_t single = sizeof(ws_header) + tile_state<rbk_pair<unsigned, V>>::bytes(tiles + 1);
+  if constexpr (sizeof(K) == sizeof(V) && (sizeof(K) == 4 || sizeof(K) == 8)) {
+    const size_t stream = rbk_stream_workspace_bytes<K, V>(n);
+    return single > stream ? single : stream;
+  }
+  return single;
 }
 
 // Launches the segmented scan; no sync.  out may be vals (in place).  n < 2^32 * tile size.
@@ -124,7 +129,19 @@ cudaError_t scan_by_key_async(KeyIt keys, ValIt vals, OutIt out, size_t n, K, V 
   ws_header* hdr = reinterpret_cast<ws_header*>(base);
   constexpr int IPT = rbk_tuning<K, V>::IPT;
   const size_t tiles = (n + rbk_tile_items<K, V>() - 1) / rbk_tile_items<K, V>();
-  cudaError_t e = cudaMemsetAsync(base, 0, n ? scan_by_key_workspace_bytes<K, V>(n) : sizeof(ws_header), stream);
+  // large contiguous inputs with keys and values of one size: the two-pass streaming kernels
+  // (reduce_by_key_stream.cuh)
+  if constexpr (std::is_pointer<KeyIt>::value && std::is_pointer<ValIt>::value && std::is_pointer<OutIt>::value && sizeof(K) == sizeof(V) &&
+                (sizeof(K) == 4 || sizeof(K) == 8) && std::is_trivially_copyable<K>::value && std::is_trivially_copyable<V>::value) {
+    using KIn = typename std::remove_cv<typename std::remove_pointer<KeyIt>::type>::type;
+    using VIn = typename std::remove_cv<typename std::remove_pointer<ValIt>::type>::type;
+    using VOut = typename std::remove_pointer<OutIt>::type;
+    if constexpr (std::is_same<KIn, K>::value && std::is_same<VIn, V>::value && std::is_same<VOut, V>::value) {
+      if (scan_by_key_stream_eligible(keys, vals, out, n, sizeof(K)))
+        return scan_by_key_stream_async<INCLUSIVE, K, V, Eq, Op>(keys, vals, out, n, init, eq, op, ws, stream);
+    }
+  }
+  cudaError_t e = cudaMemsetAsync(base, 0, n ? sizeof(ws_header) + tile_state<rbk_pair<unsigned, V>>::bytes(tiles + 1) : sizeof(ws_header), stream);
   if (e != cudaSuccess || n == 0) return e;
   tile_state<rbk_pair<unsigned, V>> ts;
   ts.bind(base + sizeof(ws_header), tiles + 1);

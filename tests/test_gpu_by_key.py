@@ -50,3 +50,24 @@ def test_by_key_types_ops_in_place(tb, port):
     got = host(tb.inclusive_scan_by_key(dev(np.zeros(300000, np.int32)), dev(f))).astype(np.float64)
     exact = np.cumsum(f.astype(np.float64))
     assert np.max(np.abs(got - exact) / np.maximum(exact, 1.0)) < 1e-5
+
+
+@pytest.mark.parametrize("kt,vt", [(np.int32, np.int32), (np.uint32, np.float32), (np.int64, np.int64), (np.uint64, np.float64), (np.int32, np.int64)])
+def test_scan_by_key_large_bit_exact(tb, oracles, kt, vt):
+    """2^25 + 12345 items: keys and values of one size take the two-pass streaming kernels, mixed sizes
+    the single-pass one; the last row of the input is partial.  Floating-point values are small
+    integers here, so their sums are exact."""
+    n = (1 << 25) + 12345
+    keys = dg.run_keys(n).astype(kt)
+    vals = (dg.scan_input_i32(n, 7) % 1000).astype(vt)
+    init = np.asarray(11, dtype=vt)[()]
+    inc = host(tb.inclusive_scan_by_key(dev(keys), dev(vals)))
+    exc = host(tb.exclusive_scan_by_key(dev(keys), dev(vals), init))
+    mx = host(tb.inclusive_scan_by_key(dev(keys), dev(vals), op="max"))
+    d = dev(vals)
+    tb.inclusive_scan_by_key(dev(keys), d, out=d)                              # in place
+    for o in oracles:
+        assert np.array_equal(inc, o.scan_by_key(keys, vals))
+        assert np.array_equal(exc, o.scan_by_key(keys, vals, "plus", True, init))
+        assert np.array_equal(mx, o.scan_by_key(keys, vals, "max"))
+        assert np.array_equal(host(d), o.scan_by_key(keys, vals))
