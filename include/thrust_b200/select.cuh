@@ -195,7 +195,8 @@ cudaError_t select_async(InIt in, StIt stencil, SelIt out_sel, RejIt out_rej, si
         if constexpr (std::is_same<Rej, T>::value) rej = out_rej; else ok = false;
       }
       if (ok && select_stream_eligible(in, out_sel, rej, KEEP_REJECTS && !mirrored, n, sizeof(T)))
-        return select_stream_async<MODE == SEL_UNIQUE, KEEP_REJECTS, T, Pred>(in, out_sel, rej, n, pred, mirrored, d_count, ws, stream);
+        return select_stream_async<MODE == SEL_UNIQUE, KEEP_REJECTS, T, Pred>(in, out_sel, rej, n, pred, mirrored ? SELECT_REJ_MIRRORED : SELECT_REJ_SECOND_ARRAY, d_count, ws,
+                                                                              stream);
     }
   }
   cudaError_t e = cudaMemsetAsync(base, 0, sizeof(ws_header) + tile_state<unsigned long long>::bytes(tiles + 1), stream);
@@ -234,19 +235,24 @@ cudaError_t partition_finish_async(T* data, const T* scratch, size_t n, const vo
   return cudaGetLastError();
 }
 
+// The in-place partition through the streaming kernels only (the caller has checked
+// select_stream_eligible()): they know the number of kept items before they scatter, so the dropped
+// items land behind the kept ones in input order and the way back is a plain copy.
+template <class T, class Pred>
+cudaError_t partition_inplace_stream_async(T* data, T* scratch, size_t n, Pred pred, unsigned long long* d_count, void* ws, cudaStream_t stream) {
+  cudaError_t e = select_stream_async<false, true, T, Pred>((const T*)data, scratch, (T*)nullptr, n, pred, SELECT_REJ_BEHIND_SELECTED, d_count, ws, stream);
+  if (e != cudaSuccess) return e;
+  return cudaMemcpyAsync(data, scratch, n * sizeof(T), cudaMemcpyDeviceToDevice, stream);
+}
+
 // In-place stable partition of data[0, n): `scratch` holds n items.
 template <bool ALLOW_STREAM = true, class T, class Pred>
 cudaError_t partition_inplace_async(T* data, T* scratch, size_t n, Pred pred, unsigned long long* d_count, void* ws, cudaStream_t stream) {
-  cudaError_t e = select_async<SEL_PRED, true, ALLOW_STREAM>((const T*)data, (const T*)nullptr, scratch, (T*)nullptr, n, T(), pred, true, d_count, ws, stream);
+  if constexpr (ALLOW_STREAM && std::is_arithmetic<T>::value && (sizeof(T) == 4 || sizeof(T) == 8)) {
+    if (select_stream_eligible(data, scratch, nullptr, false, n, sizeof(T))) return partition_inplace_stream_async(data, scratch, n, pred, d_count, ws, stream);
+  }
+  cudaError_t e = select_async<SEL_PRED, true, false>((const T*)data, (const T*)nullptr, scratch, (T*)nullptr, n, T(), pred, true, d_count, ws, stream);
   if (e != cudaSuccess || n == 0) return e;
-  return partition_finish_async(data, scratch, n, ws, stream);
-}
-
-// The same through the streaming kernels only (the caller has checked select_stream_eligible()).
-template <class T, class Pred>
-cudaError_t partition_inplace_stream_async(T* data, T* scratch, size_t n, Pred pred, unsigned long long* d_count, void* ws, cudaStream_t stream) {
-  cudaError_t e = select_stream_async<false, true, T, Pred>((const T*)data, scratch, (T*)nullptr, n, pred, true, d_count, ws, stream);
-  if (e != cudaSuccess) return e;
   return partition_finish_async(data, scratch, n, ws, stream);
 }
 

@@ -24,6 +24,10 @@
 
 namespace tb200 {
 
+// where dropped items go (KEEP_REJECTS): a second array in input order; mirrored from the end of
+// out_sel; or behind the kept items in out_sel, in input order
+enum : int { SELECT_REJ_SECOND_ARRAY = 0, SELECT_REJ_MIRRORED = 1, SELECT_REJ_BEHIND_SELECTED = 2 };
+
 constexpr int SELECT_STREAM_BLOCK = 256;
 constexpr int SELECT_STREAM_CTAS_PER_SM = 5;   // 48 registers; 4 and 6 measured 2-4 % slower
 // below this the three launches cost more than they save (2^22 items: 0.040 ms against 0.030 single-pass)
@@ -116,7 +120,7 @@ __global__ void select_total_kernel(const unsigned long long* batch_counts, cons
 template <bool UNIQUE, bool KEEP_REJECTS, class T, class Pred, int VEC>
 __global__ void __launch_bounds__(SELECT_STREAM_BLOCK, SELECT_STREAM_CTAS_PER_SM)
 select_scatter_kernel(const T* in, T* out_sel, T* out_rej, size_t n, size_t rows, size_t batches, Pred pred, const unsigned long long* batch_offsets,
-                      bool mirrored) {
+                      int rej_mode, const ws_header* hdr) {
   const int lane = lane_id();
   const size_t gwarp = ((size_t)blockIdx.x * SELECT_STREAM_BLOCK + threadIdx.x) >> 5;
   const size_t nwarps = ((size_t)gridDim.x * SELECT_STREAM_BLOCK) >> 5;
@@ -161,7 +165,9 @@ select_scatter_kernel(const T* in, T* out_sel, T* out_rej, size_t n, size_t rows
         if (idx < row_total) out_sel[kept + idx] = buf[idx];
         else if (KEEP_REJECTS && idx < row_n) {
           const size_t r = rej_base + (idx - row_total);
-          if (mirrored) out_sel[n - 1 - r] = buf[idx]; else out_rej[r] = buf[idx];
+          if (rej_mode == SELECT_REJ_SECOND_ARRAY) out_rej[r] = buf[idx];
+          else if (rej_mode == SELECT_REJ_MIRRORED) out_sel[n - 1 - r] = buf[idx];
+          else out_sel[(size_t)hdr->count + r] = buf[idx];   // the total was published before this kernel started
         }
       }
       __syncwarp();
@@ -196,7 +202,7 @@ inline bool select_stream_eligible(const void* in, const void* out_sel, const vo
 
 // The caller has checked select_stream_eligible().
 template <bool UNIQUE, bool KEEP_REJECTS, class T, class Pred>
-cudaError_t select_stream_async(const T* in, T* out_sel, T* out_rej, size_t n, Pred pred, bool mirrored, unsigned long long* d_count, void* ws,
+cudaError_t select_stream_async(const T* in, T* out_sel, T* out_rej, size_t n, Pred pred, int rej_mode, unsigned long long* d_count, void* ws,
                                 cudaStream_t stream) {
   constexpr int VEC = 16 / sizeof(T);
   char* base = static_cast<char*>(ws);
@@ -218,7 +224,7 @@ cudaError_t select_stream_async(const T* in, T* out_sel, T* out_rej, size_t n, P
   if ((e = cudaMemsetAsync(hdr, 0, sizeof(ws_header), stream)) != cudaSuccess) return e;
   select_total_kernel<><<<1, 1, 0, stream>>>(counts, offsets, batches, hdr, static_cast<const ws_header*>(scan_ws), d_count);
   select_scatter_kernel<UNIQUE, KEEP_REJECTS, T, Pred, VEC>
-      <<<(unsigned)ctas, SELECT_STREAM_BLOCK, 0, stream>>>(in, out_sel, out_rej, n, rows, batches, pred, offsets, mirrored);
+      <<<(unsigned)ctas, SELECT_STREAM_BLOCK, 0, stream>>>(in, out_sel, out_rej, n, rows, batches, pred, offsets, rej_mode, hdr);
   return cudaGetLastError();
 }
 
