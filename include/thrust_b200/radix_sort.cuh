@@ -29,7 +29,11 @@ namespace tb200 {
 constexpr int RADIX_BITS = 8;
 constexpr int RADIX_BINS = 256;
 constexpr int RADIX_MAX_PASSES = 8;
-constexpr int ONESWEEP_BLOCK = 512;   // two CTAs per SM; 256- and 384-thread variants measured 4-15 % slower
+#ifndef TB200_SWEEP_BLOCK
+#define TB200_SWEEP_BLOCK 512
+#endif
+constexpr int ONESWEEP_BLOCK = TB200_SWEEP_BLOCK;
+constexpr int ONESWEEP_CTAS_PER_SM = 1024 / ONESWEEP_BLOCK;
 constexpr int HIST_BLOCK = 1024;
 
 enum key_kind : int { KEY_UNSIGNED = 0, KEY_SIGNED = 1, KEY_FLOAT = 2 };
@@ -151,16 +155,22 @@ radix_scan_hist_kernel(radix_ctrl* ctrl, size_t n, int first_pass) {
 }
 
 // ---------------------------------------------------------------- 3. one digit place
+#ifndef TB200_SWEEP_IPT_44
+#define TB200_SWEEP_IPT_44 16
+#endif
+#ifndef TB200_SWEEP_MATCH_EVERY
+#define TB200_SWEEP_MATCH_EVERY 0
+#endif
 template <int KB, int VB> struct onesweep_tuning {
   // items per thread; two 512-thread CTAs per SM (64 registers per thread, ~80 KB of staging each)
-  static constexpr int IPT = KB <= 4 ? (VB == 0 ? 18 : VB <= 4 ? 16 : 12) : (VB == 0 ? 12 : VB <= 4 ? 10 : 8);
+  static constexpr int IPT = KB <= 4 ? (VB == 0 ? 18 : VB <= 4 ? TB200_SWEEP_IPT_44 : 12) : (VB == 0 ? 12 : VB <= 4 ? 10 : 8);
 };
 
 // What distinguishes a radix digit pass from the multi-GPU bucket scatter: how a key maps to one of
 // up to 256 bins and where a bin's items go.
 template <class UK, class UV, bool IS_FLOAT> struct radix_pass_policy {
   static constexpr int BITS = RADIX_BITS;       // ballots per key
-  static constexpr int MATCH_EVERY = 3;         // every third key is ranked with match.any instead
+  static constexpr int MATCH_EVERY = TB200_SWEEP_MATCH_EVERY;   // every third row is ranked with match.any instead
   UK* dst; UV* vdst; int shift; unsigned dmask;
   __device__ __forceinline__ unsigned digit(UK k) const { return key_digit<IS_FLOAT>(k, shift, dmask); }
   __device__ __forceinline__ UK* keys_of(unsigned) const { return dst; }
@@ -195,96 +205,189 @@ template <class UK, class UV> struct bucket_policy {
   __device__ __forceinline__ UV* vals_of(unsigned d) const { return dst_v[d]; }
 };
 
+// Tunables of the tile routine (overridable on the compiler's command line for experiments).
+// Tunables of the tile routine (overridable on the compiler's command line for experiments).
+#ifndef TB200_SWEEP_LATE_CLAIM
+#define TB200_SWEEP_LATE_CLAIM 0    // 1: the next tile is claimed after the staging instead of after the ranking
+#endif
+#ifndef TB200_SWEEP_LB_BATCH
+#define TB200_SWEEP_LB_BATCH 4      // descriptors fetched per round trip of the look-back
+#endif
+#ifndef TB200_SWEEP_LOOP_MAX
+#define TB200_SWEEP_LOOP_MAX 6      // rows with more colliding lanes than this are ranked with ballots
+#endif
+
+// Staged item: a key and its value side by side, so that one shared-memory store / load moves both.
+template <class UK, class UV, bool HAS_V, bool PACKED> struct sweep_stage;
+template <class UK, class UV> struct sweep_stage<UK, UV, true, true> {   // sizeof(UK) == sizeof(UV)
+  struct __align__(2 * sizeof(UK)) item { UK k; UV v; };
+  item* slots;
+  __device__ __forceinline__ sweep_stage(unsigned char* base, int) : slots(reinterpret_cast<item*>(base)) {}
+  __device__ __forceinline__ void put(unsigned p, UK k, UV v) const { item it; it.k = k; it.v = v; slots[p] = it; }
+  __device__ __forceinline__ void get(unsigned p, UK& k, UV& v) const { const item it = slots[p]; k = it.k; v = it.v; }
+};
+template <class UK, class UV> struct sweep_stage<UK, UV, true, false> {
+  UK* ks; UV* vs;
+  __device__ __forceinline__ sweep_stage(unsigned char* base, int tile_items)
+      : ks(reinterpret_cast<UK*>(sizeof(UK) >= sizeof(UV) ? base : base + (size_t)tile_items * sizeof(UV))),
+        vs(reinterpret_cast<UV*>(sizeof(UK) >= sizeof(UV) ? base + (size_t)tile_items * sizeof(UK) : base)) {}
+  __device__ __forceinline__ void put(unsigned p, UK k, UV v) const { ks[p] = k; vs[p] = v; }
+  __device__ __forceinline__ void get(unsigned p, UK& k, UV& v) const { k = ks[p]; v = vs[p]; }
+};
+template <class UK, class UV, bool PACKED> struct sweep_stage<UK, UV, false, PACKED> {
+  UK* ks;
+  __device__ __forceinline__ sweep_stage(unsigned char* base, int) : ks(reinterpret_cast<UK*>(base)) {}
+  __device__ __forceinline__ void put(unsigned p, UK k, UV) const { ks[p] = k; }
+  __device__ __forceinline__ void get(unsigned p, UK& k, UV&) const { k = ks[p]; }
+};
+
+// A tile's items in registers, lane-interleaved inside each warp's chunk (item i of lane l is element
+// warp * 32 * IPT + i * 32 + l of the tile, so a warp-wide load instruction is contiguous).
+template <class UK, class UV, bool HAS_V, int IPT> struct sweep_regs { UK key[IPT]; UV val[HAS_V ? IPT : 1]; };
+
+template <class UK, class UV, bool HAS_V, int IPT, bool FULL>
+__device__ __forceinline__ void sweep_load(sweep_regs<UK, UV, HAS_V, IPT>& r, const UK* __restrict__ src, const UV* __restrict__ vsrc, unsigned n,
+                                           unsigned tile) {
+  constexpr int TILE = ONESWEEP_BLOCK * IPT;
+  const unsigned tile_base = tile * (unsigned)TILE;
+  const unsigned tile_n = FULL ? (unsigned)TILE : n - tile_base;
+  const unsigned wofs = (threadIdx.x >> 5) * (32 * IPT) + (threadIdx.x & 31);
+  const UK* ks = src + tile_base + wofs;
+#pragma unroll
+  for (int i = 0; i < IPT; ++i) r.key[i] = (FULL || wofs + i * 32 < tile_n) ? __ldcs(ks + i * 32) : (UK)0;
+  if constexpr (HAS_V) {
+    const UV* vs = vsrc + tile_base + wofs;
+#pragma unroll
+    for (int i = 0; i < IPT; ++i) r.val[i] = (FULL || wofs + i * 32 < tile_n) ? __ldcs(vs + i * 32) : (UV)0;
+  }
+}
+template <class UK, class UV, bool HAS_V, int IPT>
+__device__ __forceinline__ void sweep_load_any(sweep_regs<UK, UV, HAS_V, IPT>& r, const UK* __restrict__ src, const UV* __restrict__ vsrc, unsigned n,
+                                               unsigned tile) {
+  if ((unsigned long long)(tile + 1) * (ONESWEEP_BLOCK * IPT) <= n) sweep_load<UK, UV, HAS_V, IPT, true>(r, src, vsrc, n, tile);
+  else sweep_load<UK, UV, HAS_V, IPT, false>(r, src, vsrc, n, tile);
+}
+
+// One tile of a digit pass: ranks the tile's keys (held in `r`) by digit, chains the per-digit
+// counts to the preceding tiles and writes keys and values to their buckets.  Once the items are
+// staged in shared memory the registers are free, so the NEXT tile of this CTA (`next`, if
+// `next < num_tiles`) is loaded into them while this one is chained and written out.
+//
+// Ranking.  Every lane adds 1 to its warp's private counter of its digit and then reads the counter
+// back: `old` is some slot of the digit's group in this row, `now - old > 1` tells all members of a
+// group of two or more lanes, except the one that drew the last slot, that they collided.  Lanes
+// that did not collide are done (rank = old).  Groups are then put in lane order one at a time: the
+// highest colliding lane announces its digit, one ballot finds its group, each member takes
+// base + (members in lower lanes).  With 256 bins and 32 lanes a row has about two groups, which
+// costs half the instructions of finding every lane's peers with one ballot per digit bit; rows
+// with more than TB200_SWEEP_LOOP_MAX colliding lanes (skewed digits, the padded last tile) take
+// the ballots.  The result does not depend on the order in which the hardware serves the atomics.
 template <class UK, class UV, bool HAS_V, class Policy, class LB, int IPT, bool FULL>
-__device__ __forceinline__ void onesweep_tile(const UK* __restrict__ src, const UV* __restrict__ vsrc, unsigned n, unsigned tile, const Policy policy,
-                                              const unsigned long long* bin_base, LB* lookback, unsigned* err,
-                                              unsigned* warp_hist, unsigned* s_goff, unsigned* s_scan, UK* stage_k, UV* stage_v) {
+__device__ __forceinline__ void onesweep_tile(sweep_regs<UK, UV, HAS_V, IPT>& r, const UK* __restrict__ src, const UV* __restrict__ vsrc, unsigned n,
+                                              unsigned tile, unsigned num_tiles, unsigned* next_ticket, unsigned& next, const Policy policy,
+                                              unsigned my_bin_base, LB* lookback, unsigned* err, unsigned* warp_hist, unsigned* s_goff,
+                                              unsigned* s_scan, unsigned* s_next, unsigned char* stage_raw) {
   constexpr int NWARPS = ONESWEEP_BLOCK / 32;
   constexpr int TILE = ONESWEEP_BLOCK * IPT;
   constexpr int WCHUNK = 32 * IPT;
   constexpr int LB_BITS = 8 * sizeof(LB) - 2;
   constexpr LB LB_MASK = ((LB)1 << LB_BITS) - 1;
+  constexpr LB F_VALID = (LB)1 << LB_BITS, F_INC = (LB)2 << LB_BITS;   // a tile's count: valid; an inclusive prefix: valid | inc
   constexpr int PAD_DIGIT = (1 << Policy::BITS) - 1;
+  constexpr bool PACKED = HAS_V && sizeof(UK) == sizeof(UV);
   const int lane = lane_id(), warp = threadIdx.x >> 5;
   const unsigned tile_base = tile * (unsigned)TILE;
   const unsigned tile_n = FULL ? (unsigned)TILE : n - tile_base;
   const unsigned wofs = warp * WCHUNK + lane;   // this lane's first item inside the tile
 
-  // ---- load keys, lane-interleaved inside the warp's chunk (a warp instruction is contiguous)
-  UK key[IPT];
-  const UK* ksrc = src + tile_base + wofs;
-#pragma unroll
-  for (int i = 0; i < IPT; ++i) key[i] = (FULL || wofs + i * 32 < tile_n) ? __ldcs(ksrc + i * 32) : (UK)0;
-
-  // ---- rank inside the warp: keys of equal digit find each other with ballots; the first
-  // lane of each group reserves the group's slots in the warp's private digit counters
+  // ---- rank inside the warp
   unsigned pd[IPT];   // low 16 bits: position, bits 16..23: digit
   unsigned* my_hist = warp_hist + warp * RADIX_BINS;
-  const unsigned lanemask_lt = (1u << lane) - 1;
+  const unsigned lanemask_lt = (1u << lane) - 1, lanemask_ge = ~lanemask_lt;
 #pragma unroll
   for (int i = 0; i < IPT; ++i) {
     // a partial tile pads with pseudo-keys of the highest digit: ranked after every real key of the tile
-    unsigned d = (FULL || wofs + i * 32 < tile_n) ? policy.digit(key[i]) : (unsigned)PAD_DIGIT;
-    // lanes holding the same digit: one ballot per digit bit.  Every MATCH_EVERY-th key asks the
-    // match unit instead: it runs beside the ALU pipe that the ballots load, but at a small fraction
-    // of their rate on sm_100, so it can only take a share of the keys.
-    unsigned peers;
+    const unsigned d = (FULL || wofs + i * 32 < tile_n) ? policy.digit(r.key[i]) : (unsigned)PAD_DIGIT;
+    unsigned rank;
     if (Policy::MATCH_EVERY != 0 && (i + 1) % (Policy::MATCH_EVERY != 0 ? Policy::MATCH_EVERY : 1) == 0) {
-      peers = __match_any_sync(FULL_MASK, d);
+      // the match unit runs beside the ALU pipe, but at a small fraction of its rate on sm_100
+      const unsigned peers = __match_any_sync(FULL_MASK, d);
+      const unsigned ahead = __popc(peers & lanemask_lt);
+      unsigned before = 0;
+      if (ahead == 0) before = atomicAdd(&my_hist[d], (unsigned)__popc(peers));
+      rank = __shfl_sync(FULL_MASK, before, __ffs(peers) - 1) + ahead;
     } else {
-      peers = FULL_MASK;
+      const unsigned old = atomicAdd(&my_hist[d], 1u);
+      __syncwarp();   // every lane's increment precedes every lane's read
+      const unsigned now = *reinterpret_cast<volatile unsigned*>(&my_hist[d]);
+      unsigned pending = __ballot_sync(FULL_MASK, now - old > 1u);
+      rank = old;
+      if (Policy::BITS > 4 && __popc(pending) <= TB200_SWEEP_LOOP_MAX) {
+        while (pending) {
+          const unsigned dsrc = __shfl_sync(FULL_MASK, d, 31 - __clz(pending));
+          const unsigned peers = __ballot_sync(FULL_MASK, d == dsrc);
+          if (d == dsrc) rank = now - __popc(peers & lanemask_ge);   // base + members in lower lanes
+          pending &= ~peers;
+        }
+      } else if (pending) {
+        unsigned peers = FULL_MASK;
 #pragma unroll
-      for (int b = 0; b < Policy::BITS; ++b) {
-        const bool bit = (d >> b) & 1;
-        const unsigned vote = __ballot_sync(FULL_MASK, bit);
-        peers &= bit ? vote : ~vote;
+        for (int b = 0; b < Policy::BITS; ++b) {
+          const bool bit = (d >> b) & 1;
+          const unsigned vote = __ballot_sync(FULL_MASK, bit);
+          peers &= bit ? vote : ~vote;
+        }
+        rank = now - __popc(peers & lanemask_ge);
       }
     }
-    const unsigned ahead = __popc(peers & lanemask_lt);
-    unsigned before = 0;
-    if (ahead == 0) before = atomicAdd(&my_hist[d], (unsigned)__popc(peers));
-    before = __shfl_sync(FULL_MASK, before, __ffs(peers) - 1);
-    pd[i] = (before + ahead) | (d << 16);
+    pd[i] = rank | (d << 16);
   }
   __syncthreads();
 
-  // ---- per digit: stack the warps' counts, scan the digits, chain to the preceding tiles
+  // ---- per digit: stack the warps' counts, scan the digits
+  if (!TB200_SWEEP_LATE_CLAIM && threadIdx.x == 0) *s_next = atomicAdd(next_ticket, 1u);
   unsigned my_count = 0, digit_off = 0;
+  LB* const slot = lookback + (size_t)tile * RADIX_BINS + (threadIdx.x & (RADIX_BINS - 1));
   if (threadIdx.x < RADIX_BINS) {
     unsigned run = 0;
 #pragma unroll
     for (int w = 0; w < NWARPS; ++w) { unsigned c = warp_hist[w * RADIX_BINS + threadIdx.x]; warp_hist[w * RADIX_BINS + threadIdx.x] = run; run += c; }
     my_count = run;
-    unsigned incl = warp_inclusive_scan(my_count, plus_op());
+    if (!FULL && threadIdx.x == PAD_DIGIT) my_count -= (unsigned)TILE - tile_n;
+    // the tile's own count is visible to its successors before anything else happens
+    *reinterpret_cast<volatile LB*>(slot) = (tile == 0 ? (F_VALID | F_INC) : F_VALID) | (LB)my_count;
+    const unsigned incl = warp_inclusive_scan(run, plus_op());
     if (lane == 31) s_scan[warp] = incl;
-    digit_off = incl - my_count;
+    digit_off = incl - run;
   }
   __syncthreads();
-  unsigned real_count = 0;
-  LB* const slot = lookback + (size_t)tile * RADIX_BINS + (threadIdx.x & (RADIX_BINS - 1));
   if (threadIdx.x < RADIX_BINS) {
     for (int w = 0; w < warp; ++w) digit_off += s_scan[w];
-    real_count = my_count;
-    if (!FULL && threadIdx.x == PAD_DIGIT) real_count -= (unsigned)TILE - tile_n;
-    // the tile's own count is visible to its successors before anything else happens
-    *reinterpret_cast<volatile LB*>(slot) = ((LB)(tile == 0 ? TILE_INCLUSIVE : TILE_AGGREGATE) << LB_BITS) | (LB)real_count;
 #pragma unroll
     for (int w = 0; w < NWARPS; ++w) warp_hist[w * RADIX_BINS + threadIdx.x] += digit_off;
   }
   __syncthreads();
 
-  // ---- stage keys in bucket order; fetch the values while the keys stream out
+  // ---- stage keys and values in bucket order; the registers then take the CTA's next tile
+  const sweep_stage<UK, UV, HAS_V, PACKED> stage(stage_raw, TILE);
 #pragma unroll
   for (int i = 0; i < IPT; ++i) {
-    unsigned p = (pd[i] & 0xffffu) + my_hist[pd[i] >> 16];
-    pd[i] = p;
-    stage_k[p] = key[i];
+    const unsigned p = (pd[i] & 0xffffu) + my_hist[pd[i] >> 16];
+    stage.put(p, r.key[i], r.val[HAS_V ? i : 0]);
   }
-  UV val[HAS_V ? IPT : 1];
-  if constexpr (HAS_V) {
-    const UV* vs = vsrc + tile_base + wofs;
+  if (TB200_SWEEP_LATE_CLAIM) {
+    // claimed as late as the prefetch allows: tiles should start in the order in which they are claimed
+    if (threadIdx.x == 0) *s_next = atomicAdd(next_ticket, 1u);
+  } else {
+    next = *s_next;
+    if (next < num_tiles) sweep_load_any<UK, UV, HAS_V, IPT>(r, src, vsrc, n, next);
+  }
+  __syncwarp();
+  // each warp clears its own counters for its next tile (nobody else touches them until the next stacking)
+  {
+    uint4* z = reinterpret_cast<uint4*>(my_hist);
 #pragma unroll
-    for (int i = 0; i < IPT; ++i) val[i] = (FULL || wofs + i * 32 < tile_n) ? __ldcs(vs + i * 32) : (UV)0;
+    for (int q = 0; q < RADIX_BINS / 4 / 32; ++q) z[q * 32 + lane] = make_uint4(0, 0, 0, 0);
   }
 
   // ---- chain to the preceding tiles, one thread per digit.  The preceding tiles had the time of
@@ -293,7 +396,7 @@ __device__ __forceinline__ void onesweep_tile(const UK* __restrict__ src, const 
   if (threadIdx.x < RADIX_BINS) {
     LB prefix = 0;
     if (tile != 0) {
-      constexpr int LB_BATCH = 4;   // 2..6 measured alike, 8 and 16 slower
+      constexpr int LB_BATCH = TB200_SWEEP_LB_BATCH;
       long long t = (long long)tile - 1;   // nearest tile not yet accounted for
       unsigned iter = 0;
       bool done = false;
@@ -304,15 +407,14 @@ __device__ __forceinline__ void onesweep_tile(const UK* __restrict__ src, const 
           const long long tj = t - j > 0 ? t - j : 0;
           w[j] = *reinterpret_cast<const volatile LB*>(lookback + (size_t)tj * RADIX_BINS + threadIdx.x);
         }
-        bool stop = false;
+        bool open = true;
         int taken = 0;
 #pragma unroll
         for (int j = 0; j < LB_BATCH; ++j) {
-          const unsigned st = (unsigned)(w[j] >> LB_BITS);
-          const bool take = !stop && st != TILE_INVALID;
+          const bool take = open && (w[j] & F_VALID) != 0;
           if (take) { prefix += w[j] & LB_MASK; ++taken; }
-          if (take && st == TILE_INCLUSIVE) done = true;
-          stop = stop || st == TILE_INVALID || st == TILE_INCLUSIVE;
+          if (take && (w[j] & F_INC) != 0) done = true;
+          open = take && (w[j] & F_INC) == 0;
         }
         t -= taken;
         if (taken == 0) {
@@ -322,42 +424,69 @@ __device__ __forceinline__ void onesweep_tile(const UK* __restrict__ src, const 
           iter = 0;
         }
       }
-      *reinterpret_cast<volatile LB*>(slot) = ((LB)TILE_INCLUSIVE << LB_BITS) | (LB)(prefix + real_count);
+      *reinterpret_cast<volatile LB*>(slot) = F_VALID | F_INC | (prefix + (LB)my_count);
     }
-    s_goff[threadIdx.x] = (unsigned)bin_base[threadIdx.x] + (unsigned)prefix - digit_off;
+    s_goff[threadIdx.x] = my_bin_base + (unsigned)prefix - digit_off;   // bucket's global offset minus its staged offset
   }
   __syncthreads();
+  if (TB200_SWEEP_LATE_CLAIM) {
+    next = *s_next;
+    if (next < num_tiles) sweep_load_any<UK, UV, HAS_V, IPT>(r, src, vsrc, n, next);
+  }
   // consecutive threads take consecutive staged slots, so each bucket's run is written contiguously
 #pragma unroll
   for (int i = 0; i < IPT; ++i) {
-    unsigned j = threadIdx.x + i * ONESWEEP_BLOCK;
+    const unsigned j = threadIdx.x + i * ONESWEEP_BLOCK;
     if (FULL || j < tile_n) {
-      UK k = stage_k[j];
+      UK k; UV v;
+      stage.get(j, k, v);
       const unsigned d = policy.digit(k);
-      policy.keys_of(d)[s_goff[d] + j] = k;
+      const unsigned at = s_goff[d] + j;
+      policy.keys_of(d)[at] = k;
+      if constexpr (HAS_V) policy.vals_of(d)[at] = v;
     }
   }
-  if constexpr (HAS_V) {
-#pragma unroll
-    for (int i = 0; i < IPT; ++i) stage_v[pd[i]] = val[i];
-    __syncthreads();
-#pragma unroll
-    for (int i = 0; i < IPT; ++i) {
-      unsigned j = threadIdx.x + i * ONESWEEP_BLOCK;
-      if (FULL || j < tile_n) {
-        const unsigned d = policy.digit(stage_k[j]);
-        policy.vals_of(d)[s_goff[d] + j] = stage_v[j];
-      }
-    }
+  // the next tile's staging, s_goff and s_scan writes all sit behind that tile's own barriers,
+  // which every warp reaches only after it has finished the stores above
+}
+
+// The persistent loop shared by the digit pass and the bucket scatter: tiles are handed out by an
+// atomic ticket in increasing order (which is what lets a tile wait for its predecessors), every CTA
+// keeps the tile after its current one in flight in registers.
+template <class UK, class UV, bool HAS_V, class Policy, class LB, int IPT>
+__device__ __forceinline__ void sweep_tiles(const UK* __restrict__ src, const UV* __restrict__ vsrc, unsigned n, unsigned* ticket, const Policy policy,
+                                            unsigned my_bin_base, LB* lookback, unsigned* err, unsigned char* smem_raw) {
+  constexpr int NWARPS = ONESWEEP_BLOCK / 32;
+  constexpr int TILE = ONESWEEP_BLOCK * IPT;
+  unsigned* warp_hist = reinterpret_cast<unsigned*>(smem_raw);   // [NWARPS][256]
+  unsigned* s_goff = warp_hist + NWARPS * RADIX_BINS;            // [256]
+  unsigned* s_scan = s_goff + RADIX_BINS;                        // [16]
+  unsigned char* stage_raw = reinterpret_cast<unsigned char*>(s_scan + 16);
+  __shared__ unsigned s_next;
+  const unsigned num_tiles = (unsigned)(((unsigned long long)n + TILE - 1) / TILE);
+
+  if (threadIdx.x == 0) s_next = atomicAdd(ticket, 1u);
+  for (int i = threadIdx.x; i < NWARPS * RADIX_BINS; i += ONESWEEP_BLOCK) warp_hist[i] = 0;
+  __syncthreads();
+  unsigned tile = s_next;
+  sweep_regs<UK, UV, HAS_V, IPT> r;
+  if (tile < num_tiles) sweep_load_any<UK, UV, HAS_V, IPT>(r, src, vsrc, n, tile);
+  while (tile < num_tiles) {
+    unsigned next;
+    if ((unsigned long long)(tile + 1) * TILE <= n)
+      onesweep_tile<UK, UV, HAS_V, Policy, LB, IPT, true>(r, src, vsrc, n, tile, num_tiles, ticket, next, policy, my_bin_base, lookback, err, warp_hist,
+                                                          s_goff, s_scan, &s_next, stage_raw);
+    else
+      onesweep_tile<UK, UV, HAS_V, Policy, LB, IPT, false>(r, src, vsrc, n, tile, num_tiles, ticket, next, policy, my_bin_base, lookback, err, warp_hist,
+                                                           s_goff, s_scan, &s_next, stage_raw);
+    tile = next;
   }
 }
 
 template <class UK, class UV, bool HAS_V, bool IS_FLOAT, class LB, int IPT>
-__global__ void __launch_bounds__(ONESWEEP_BLOCK, 2)
+__global__ void __launch_bounds__(ONESWEEP_BLOCK, ONESWEEP_CTAS_PER_SM)
 onesweep_kernel(UK* buf_a, UK* buf_b, UV* val_a, UV* val_b, unsigned n, key_coding coding, int pass, int first_pass,
-                radix_ctrl* ctrl, LB* lookback, ws_header* hdr, unsigned prefetch_tiles) {
-  constexpr int NWARPS = ONESWEEP_BLOCK / 32;
-  constexpr int TILE = ONESWEEP_BLOCK * IPT;
+                radix_ctrl* ctrl, LB* lookback, ws_header* hdr) {
   if (ctrl->skip[pass]) return;
   int flips = 0;
   for (int q = first_pass; q < pass; ++q) flips += ctrl->skip[q] ? 0 : 1;
@@ -365,41 +494,12 @@ onesweep_kernel(UK* buf_a, UK* buf_b, UV* val_a, UV* val_b, unsigned n, key_codi
   UK* dst = (flips & 1) ? buf_a : buf_b;
   const UV* vsrc = (flips & 1) ? val_b : val_a;
   UV* vdst = (flips & 1) ? val_a : val_b;
-
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  unsigned* warp_hist = reinterpret_cast<unsigned*>(smem_raw);   // [NWARPS][256]
-  unsigned* s_goff = warp_hist + NWARPS * RADIX_BINS;   // [256] bucket's global offset minus its staged offset
-  unsigned* s_scan = s_goff + RADIX_BINS;                         // [16]
-  UK* stage_k = reinterpret_cast<UK*>(s_scan + 16);
-  UV* stage_v = reinterpret_cast<UV*>(stage_k + TILE);
-  __shared__ unsigned s_tile;
-
-  if (threadIdx.x == 0) s_tile = atomicAdd(&ctrl->tickets[pass], 1u);
-  for (int i = threadIdx.x; i < NWARPS * RADIX_BINS; i += ONESWEEP_BLOCK) warp_hist[i] = 0;
-  __syncthreads();
-  const unsigned tile = s_tile;
-  // Ask L2 for the tile that a CTA of the next wave will take, so that its loads find the data
-  // on chip.  (A hint only: needs a 16-byte aligned address, skipped otherwise.)
-  if (threadIdx.x == 32 && prefetch_tiles != 0) {
-    const unsigned long long ahead = (unsigned long long)(tile + prefetch_tiles) * TILE;
-    if (ahead + TILE <= n) {
-      if ((reinterpret_cast<unsigned long long>(src + ahead) & 15) == 0)
-        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src + ahead), "r"((unsigned)(TILE * sizeof(UK))) : "memory");
-      if (HAS_V && (reinterpret_cast<unsigned long long>(vsrc + ahead) & 15) == 0)
-        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(vsrc + ahead), "r"((unsigned)(TILE * sizeof(UV))) : "memory");
-    }
-  }
   const int shift = pass * RADIX_BITS;
-  const unsigned dmask = digit_mask<UK>(coding, shift);
-  const bool full = (unsigned long long)(tile + 1) * TILE <= n;
   using Policy = radix_pass_policy<UK, UV, IS_FLOAT>;
-  const Policy policy{dst, vdst, shift, dmask};
-  if (full)
-    onesweep_tile<UK, UV, HAS_V, Policy, LB, IPT, true>(src, vsrc, n, tile, policy, ctrl->hist[pass], lookback, &hdr->error, warp_hist, s_goff, s_scan,
-                                                        stage_k, stage_v);
-  else
-    onesweep_tile<UK, UV, HAS_V, Policy, LB, IPT, false>(src, vsrc, n, tile, policy, ctrl->hist[pass], lookback, &hdr->error, warp_hist, s_goff, s_scan,
-                                                         stage_k, stage_v);
+  const Policy policy{dst, vdst, shift, digit_mask<UK>(coding, shift)};
+  const unsigned my_bin_base = threadIdx.x < RADIX_BINS ? (unsigned)ctrl->hist[pass][threadIdx.x] : 0u;
+  sweep_tiles<UK, UV, HAS_V, Policy, LB, IPT>(src, vsrc, n, &ctrl->tickets[pass], policy, my_bin_base, lookback, &hdr->error, smem_raw);
 }
 
 // ---------------------------------------------------------------- multi-GPU: bucket count and scatter
@@ -439,40 +539,23 @@ bucket_count_kernel(const UK* keys, size_t n, key_coding coding, const UK* split
 // pass (ballot ranking, per-bin look-back, staging so that each bin's run is stored contiguously);
 // only the bin function and the destinations differ.
 template <class UK, class UV, bool HAS_V, class LB, int IPT>
-__global__ void __launch_bounds__(ONESWEEP_BLOCK, 2)
+__global__ void __launch_bounds__(ONESWEEP_BLOCK, ONESWEEP_CTAS_PER_SM)
 bucket_scatter_kernel(const UK* src, const UV* vsrc, unsigned n, key_coding coding, const UK* splitters, int buckets, bucket_table<UK, UV> table,
                       LB* lookback, ws_header* hdr) {
-  constexpr int NWARPS = ONESWEEP_BLOCK / 32;
-  constexpr int TILE = ONESWEEP_BLOCK * IPT;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  unsigned* warp_hist = reinterpret_cast<unsigned*>(smem_raw);
-  unsigned* s_goff = warp_hist + NWARPS * RADIX_BINS;
-  unsigned* s_scan = s_goff + RADIX_BINS;
-  UK* stage_k = reinterpret_cast<UK*>(s_scan + 16);
-  UV* stage_v = reinterpret_cast<UV*>(stage_k + TILE);
-  __shared__ unsigned s_tile;
   __shared__ UK s_code[MAX_BUCKETS];
   __shared__ UK* s_dst_k[MAX_BUCKETS];
   __shared__ UV* s_dst_v[MAX_BUCKETS];
-  __shared__ unsigned long long s_base[RADIX_BINS];
-
-  if (threadIdx.x == 0) s_tile = atomicAdd(&hdr->ticket, 1u);
-  for (int i = threadIdx.x; i < NWARPS * RADIX_BINS; i += ONESWEEP_BLOCK) warp_hist[i] = 0;
-  if (threadIdx.x < RADIX_BINS) s_base[threadIdx.x] = threadIdx.x < MAX_BUCKETS ? table.base[threadIdx.x] : 0ull;
   if (threadIdx.x < MAX_BUCKETS) {
     s_dst_k[threadIdx.x] = table.dst_k[threadIdx.x];
     s_dst_v[threadIdx.x] = table.dst_v[threadIdx.x];
     if ((int)threadIdx.x < buckets - 1) s_code[threadIdx.x] = key_code(splitters[threadIdx.x], coding);
   }
   __syncthreads();
-  const unsigned tile = s_tile;
   using Policy = bucket_policy<UK, UV>;
   const Policy policy{coding, buckets, s_code, s_dst_k, s_dst_v};
-  const bool full = (unsigned long long)(tile + 1) * TILE <= n;
-  if (full)
-    onesweep_tile<UK, UV, HAS_V, Policy, LB, IPT, true>(src, vsrc, n, tile, policy, s_base, lookback, &hdr->error, warp_hist, s_goff, s_scan, stage_k, stage_v);
-  else
-    onesweep_tile<UK, UV, HAS_V, Policy, LB, IPT, false>(src, vsrc, n, tile, policy, s_base, lookback, &hdr->error, warp_hist, s_goff, s_scan, stage_k, stage_v);
+  const unsigned my_bin_base = threadIdx.x < MAX_BUCKETS ? (unsigned)table.base[threadIdx.x] : 0u;
+  sweep_tiles<UK, UV, HAS_V, Policy, LB, IPT>(src, vsrc, n, &hdr->ticket, policy, my_bin_base, lookback, &hdr->error, smem_raw);
 }
 
 // ---------------------------------------------------------------- 4. copy back after an odd number of passes
@@ -493,15 +576,16 @@ radix_copy_back_kernel(UK* buf_a, const UK* buf_b, UV* val_a, const UV* val_b, s
 // ---------------------------------------------------------------- host side
 template <int KB, int VB> constexpr int onesweep_tile_items() { return ONESWEEP_BLOCK * onesweep_tuning<KB, VB>::IPT; }
 
+// per-warp counters, bucket offsets, digit scan, tile counts, look-back window, staged items
 template <int KB, int VB> size_t onesweep_smem_bytes() {
   return (size_t)(ONESWEEP_BLOCK / 32) * RADIX_BINS * 4 + RADIX_BINS * 4 + 16 * 4 + (size_t)onesweep_tile_items<KB, VB>() * (KB + VB);
 }
 
 // scratch (not counting the alternate key/value buffers, which the caller provides)
+template <int KB, int VB> size_t sweep_tiles_of(size_t n) { return (n + onesweep_tile_items<KB, VB>() - 1) / onesweep_tile_items<KB, VB>(); }
 template <int KB, int VB> size_t radix_workspace_bytes(size_t n) {
-  size_t tiles = (n + onesweep_tile_items<KB, VB>() - 1) / onesweep_tile_items<KB, VB>();
   size_t lb_word = n < (1ull << 30) ? 4 : 8;
-  return sizeof(ws_header) + sizeof(radix_ctrl) + align_up(tiles * RADIX_BINS * lb_word, 256) * KB;
+  return sizeof(ws_header) + sizeof(radix_ctrl) + align_up(sweep_tiles_of<KB, VB>(n) * RADIX_BINS * lb_word, 256) * KB;
 }
 
 // Sorts keys (and values) held in keys_a / vals_a, in place from the caller's point of view:
@@ -518,12 +602,12 @@ cudaError_t radix_sort_async(UK* keys_a, UK* keys_b, UV* vals_a, UV* vals_b, siz
   const int first_pass = begin_bit / RADIX_BITS, num_passes = (end_bit - begin_bit) / RADIX_BITS;
   const size_t tiles = (n + onesweep_tile_items<KB, VB>() - 1) / onesweep_tile_items<KB, VB>();
   const bool lb32 = n < (1ull << 30);
-  const size_t lb_bytes = align_up(tiles * RADIX_BINS * (lb32 ? 4 : 8), 256);
+  const size_t lb_bytes = align_up(sweep_tiles_of<KB, VB>(n) * RADIX_BINS * (lb32 ? 4 : 8), 256);
   char* base = static_cast<char*>(ws);
   ws_header* hdr = reinterpret_cast<ws_header*>(base);
   radix_ctrl* ctrl = reinterpret_cast<radix_ctrl*>(base + sizeof(ws_header));
   char* lb0 = base + sizeof(ws_header) + sizeof(radix_ctrl);
-  cudaError_t e = cudaMemsetAsync(base, 0, sizeof(ws_header) + sizeof(radix_ctrl) + lb_bytes * num_passes, stream);
+  cudaError_t e = cudaMemsetAsync(base, 0, (size_t)(lb0 - base) + lb_bytes * num_passes, stream);
   if (e != cudaSuccess) return e;
 
   const device_info& di = current_device_info();
@@ -542,16 +626,18 @@ cudaError_t radix_sort_async(UK* keys_a, UK* keys_b, UV* vals_a, UV* vals_b, siz
   auto k64 = isf ? onesweep_kernel<UK, UV, HAS_V, true, unsigned long long, IPT> : onesweep_kernel<UK, UV, HAS_V, false, unsigned long long, IPT>;
   // opting in to large dynamic shared memory is per kernel and per device; it is cheap, so do it every call
   if ((e = cudaFuncSetAttribute(lb32 ? (const void*)k32 : (const void*)k64, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
-  const unsigned prefetch_tiles = 2u * (unsigned)di.sm_count;   // two CTAs are resident per SM: the next wave's tile
+  // persistent CTAs, two resident per SM; tiles are handed out by ticket
+  const size_t tiles_all = sweep_tiles_of<KB, VB>(n);
+  const unsigned grid = (unsigned)(tiles_all < (size_t)di.sm_count * ONESWEEP_CTAS_PER_SM ? tiles_all : (size_t)di.sm_count * ONESWEEP_CTAS_PER_SM);
   for (int p = 0; p < num_passes; ++p) {
     char* lb = lb0 + lb_bytes * p;
     timed_launch tl(KID_ONESWEEP, stream);
     if (lb32)
-      k32<<<(unsigned)tiles, ONESWEEP_BLOCK, smem, stream>>>(keys_a, keys_b, vals_a, vals_b, (unsigned)n, coding, first_pass + p, first_pass, ctrl,
-                                                            reinterpret_cast<uint32_t*>(lb), hdr, prefetch_tiles);
+      k32<<<grid, ONESWEEP_BLOCK, smem, stream>>>(keys_a, keys_b, vals_a, vals_b, (unsigned)n, coding, first_pass + p, first_pass, ctrl,
+                                                  reinterpret_cast<uint32_t*>(lb), hdr);
     else
-      k64<<<(unsigned)tiles, ONESWEEP_BLOCK, smem, stream>>>(keys_a, keys_b, vals_a, vals_b, (unsigned)n, coding, first_pass + p, first_pass, ctrl,
-                                                            reinterpret_cast<unsigned long long*>(lb), hdr, prefetch_tiles);
+      k64<<<grid, ONESWEEP_BLOCK, smem, stream>>>(keys_a, keys_b, vals_a, vals_b, (unsigned)n, coding, first_pass + p, first_pass, ctrl,
+                                                  reinterpret_cast<unsigned long long*>(lb), hdr);
   }
   size_t cb_grid = (n + 256 * 8 - 1) / (256 * 8);
   if (cb_grid > (size_t)di.sm_count * 8) cb_grid = (size_t)di.sm_count * 8;
@@ -573,8 +659,7 @@ cudaError_t bucket_count_async(const UK* keys, size_t n, key_coding coding, cons
 }
 
 template <int KB, int VB> size_t bucket_scatter_workspace_bytes(size_t n) {
-  size_t tiles = (n + onesweep_tile_items<KB, VB>() - 1) / onesweep_tile_items<KB, VB>();
-  return sizeof(ws_header) + align_up(tiles * RADIX_BINS * 4, 256);
+  return sizeof(ws_header) + align_up(sweep_tiles_of<KB, VB>(n) * RADIX_BINS * 4, 256);
 }
 
 // Stable scatter into up to MAX_BUCKETS destinations (see bucket_scatter_kernel); n < 2^30.  No sync.
@@ -592,8 +677,11 @@ cudaError_t bucket_scatter_async(const UK* keys, const UV* vals, size_t n, key_c
   auto kern = bucket_scatter_kernel<UK, UV, HAS_V, uint32_t, IPT>;
   const size_t smem = onesweep_smem_bytes<KB, VB>();
   if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
-  kern<<<(unsigned)tiles, ONESWEEP_BLOCK, smem, stream>>>(keys, vals, (unsigned)n, coding, d_splitters, buckets, table,
-                                                        reinterpret_cast<uint32_t*>(base + sizeof(ws_header)), reinterpret_cast<ws_header*>(base));
+  const device_info& di = current_device_info();
+  const size_t tiles_all = sweep_tiles_of<KB, VB>(n);
+  const unsigned grid = (unsigned)(tiles_all < (size_t)di.sm_count * ONESWEEP_CTAS_PER_SM ? tiles_all : (size_t)di.sm_count * ONESWEEP_CTAS_PER_SM);
+  kern<<<grid, ONESWEEP_BLOCK, smem, stream>>>(keys, vals, (unsigned)n, coding, d_splitters, buckets, table,
+                                               reinterpret_cast<uint32_t*>(base + sizeof(ws_header)), reinterpret_cast<ws_header*>(base));
   return cudaGetLastError();
 }
 
