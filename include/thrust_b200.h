@@ -190,13 +190,19 @@ int tb200_kernel_timing_read(int capacity, int* h_kernel_ids, float* h_ms, int* 
  * a stream-ordered pool's callback, in a latency-critical loop where cudaMalloc's device-wide
  * synchronisation is not acceptable, in a plug-in that receives buffers but no allocator, or when
  * its own data has already claimed all device memory.  The other entry points make such a caller
- * bring the scratch; this one brings its own: a 256 KiB array in the library's device data
+ * bring the scratch; this one brings its own: a 512 KiB array in the library's device data
  * segment, which every GPU that loads the library holds until the process exits.
  *
- * Same arguments and result as tb200_inclusive_scan minus the workspace pair.  Limit: the tile
- * descriptors must fit the array, i.e. n <= about 2^28 elements for I32/U32/F32 and n <= about
- * 2^25 for I64/U64/F64; beyond that the call does nothing and returns
- * TB200_ERR_EXCEEDS_STATIC_SCRATCH.  It calls no cudaMalloc, cudaFree or other allocating routine.
+ * Same arguments and result as tb200_inclusive_scan minus the workspace pair.  Limit: the
+ * descriptors must fit the array, i.e. n <= 536,600,576 elements (just under 2^29) for
+ * I32/U32/F32 and n <= 134,148,096 (just under 2^27) for I64/U64/F64 with the present tile sizes;
+ * tb200_inclusive_scan_static_limit(t, &max_n) reports the exact figure of the loaded library.
+ * Beyond it the call does nothing and returns TB200_ERR_EXCEEDS_STATIC_SCRATCH.  It calls no
+ * cudaMalloc, cudaFree or other allocating routine.
+ *
+ * A wait inside the kernels that runs out (see tb200_workspace_status) is recorded in the array's
+ * first word, which the caller cannot address: tb200_inclusive_scan_static_status(stream,
+ * &status) synchronises `stream` and reads it back (0 = ok, 1 = the last call's result is invalid).
  *
  * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
  * that device current) and remembers it; make that first call before starting any stream capture.
@@ -206,6 +212,8 @@ int tb200_kernel_timing_read(int capacity, int* h_kernel_ids, float* h_ms, int* 
 #define TB200_ERR_EXCEEDS_STATIC_SCRATCH 100001
 int tb200_inclusive_scan_static(const void* d_in, void* d_out, size_t n, int t, int op,
                                 const void* h_init, tb200_stream_t stream);
+int tb200_inclusive_scan_static_limit(int t, size_t* h_max_n);
+int tb200_inclusive_scan_static_status(tb200_stream_t stream, unsigned* h_status);
 
 /* Stable merge of num_runs (<= 64) sorted runs, given as host arrays of device pointers and
  * lengths, into d_keys_out / d_vals_out (sum of the lengths); ties keep the earlier run first.  A

@@ -174,6 +174,9 @@ template <class T> struct opt {
   template <class Op> __device__ __forceinline__ void append(const T& x, Op op) {  // this = this (+) x
     v = has ? op(v, x) : x; has = true;
   }
+  template <class Op> __device__ __forceinline__ void append_opt(const opt<T>& right, Op op) {  // this = this (+) right
+    if (right.has) append(right.v, op);
+  }
   template <class Op> __device__ __forceinline__ void prepend(const opt<T>& left, Op op) {  // this = left (+) this
     if (left.has) { v = has ? op(left.v, v) : left.v; has = true; }
   }

@@ -284,16 +284,287 @@ scan_chunk_kernel(const T* in, T* out, size_t n, size_t tiles, size_t tiles_per_
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Windowed route: the two passes above, but over one window of the input at a time, so that the
+// second pass finds its window in the 126 MB L2 and HBM sees every element once on the way in and
+// once on the way out (2 * sizeof(T) bytes per element again, without the single-pass convoy).
+//
+// One persistent kernel, one CTA per resident slot (`gridDim.x` CTAs, all resident: the host sizes the
+// grid from the occupancy query).  Window w is the tiles [w * G * TPC, (w + 1) * G * TPC); CTA c owns the
+// chunk of TPC consecutive tiles number c in every window.  Per window a CTA
+//   A: reduces its chunk (plain loads: the lines stay in L2) and publishes the total in a
+//      descriptor (value and status in one word);
+//   F: folds the descriptors of the whole window -- the totals of the chunks before its own give
+//      its carry, all of them the running total for the next window; the wait for a descriptor is
+//      bounded, and since A of window w + 1 is issued BEFORE F of window w, the other CTAs' totals
+//      have normally arrived long before they are asked for;
+//   B: scans its chunk front to back (evict-first loads that hit L2, streaming stores), the carry
+//      passing from tile to tile in registers.
+// Every CTA publishes A(w) before it waits for anything of window w, so the waits cannot deadlock
+// as long as all CTAs are resident; CTAs are never more than one window apart, so about two windows
+// of input and two of output are live in L2 at a time.
+#ifndef TB200_SCANW_CTAS
+#define TB200_SCANW_CTAS 4
+#endif
+constexpr int SCANW_CTAS_PER_SM = TB200_SCANW_CTAS;
+constexpr size_t SCANW_MAX_GRID = 2048;   // CTAs at most (the fold gives every thread GRID / 256 descriptors)
+#ifndef TB200_SCANW_TPC
+#define TB200_SCANW_TPC 3        // tiles per chunk: window = resident CTAs * TPC * 16 KB (28 MB on a B200; 2 and 3 measured alike, 1 and 4+ slower)
+#endif
+
+// The operators of this route have an identity, so nothing here needs the "value may be absent"
+// bookkeeping of the generic kernels: plus starts from -0.0 for floating point (x + -0.0 == x for
+// every x, signed zeros included) and 0 otherwise, min from the largest and max from the smallest value.
+template <class Op, class T> struct op_identity;
+template <class T> struct op_identity<plus_op, T> {
+  __host__ __device__ static T value() { return std::is_floating_point<T>::value ? (T)-0.0 : (T)0; }
+};
+template <class T> struct op_identity<min_op, T> {
+  __host__ __device__ static T value() {
+    if constexpr (std::is_floating_point<T>::value) return (T)INFINITY;
+    else if constexpr (std::is_signed<T>::value) return (T)(((unsigned long long)1 << (8 * sizeof(T) - 1)) - 1);
+    else return (T)~(T)0;
+  }
+};
+template <class T> struct op_identity<max_op, T> {
+  __host__ __device__ static T value() {
+    if constexpr (std::is_floating_point<T>::value) return (T)-INFINITY;
+    else if constexpr (std::is_signed<T>::value) return (T)((unsigned long long)1 << (8 * sizeof(T) - 1));
+    else return (T)0;
+  }
+};
+
+template <class T, class Op> __device__ __forceinline__ T warp_reduce_id(T x, Op op) {
+#pragma unroll
+  for (int d = 16; d >= 1; d >>= 1) x = op(x, shfl_generic(x, 0, 3, d));   // butterfly: the operators here commute
+  return x;
+}
+
+// 16-byte load that asks L2 to keep the line (it is read again shortly) / policy for it
+__device__ __forceinline__ unsigned long long l2_keep_policy() {
+  unsigned long long pol;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ vec16 load_l2_keep16(const void* p, unsigned long long pol) {
+  vec16 v;
+  asm volatile("ld.global.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p), "l"(pol));
+  return v;
+}
+
+template <class T, class Op, bool INCLUSIVE, int VEC, int IPT>
+__global__ void __launch_bounds__(SCAN_BLOCK, SCANW_CTAS_PER_SM)
+scan_window_kernel(const T* in, T* out, size_t n, size_t tiles, unsigned tiles_per_chunk, T init, bool has_init, Op op, tile_state<T> ts,
+                   ws_header* hdr) {
+  constexpr int VPT = IPT / VEC;
+  constexpr int NWARPS = SCAN_BLOCK / 32;
+  constexpr size_t WT = 32 * IPT;           // a warp's tile: each lane holds VPT 16-byte vectors, lane-interleaved
+  const T ID = op_identity<Op, T>::value();
+#ifdef TB200_SCANW_EVICT_LAST
+  const unsigned long long keep = l2_keep_policy();
+#endif
+  __shared__ T s_part[2][NWARPS];          // each warp's total of its part of the chunk, by window parity
+  __shared__ T s_fold[2][NWARPS];          // per warp: fold of the chunks before this CTA's, of all chunks
+  const int lane = lane_id(), warp = threadIdx.x >> 5;
+  const size_t G = gridDim.x, c = blockIdx.x;
+  const size_t wtiles = (n + WT - 1) / WT;
+  const size_t chunk_wtiles = (size_t)tiles_per_chunk * NWARPS;   // a CTA's chunk; warp w owns the w-th run of tiles_per_chunk warp tiles
+  const size_t windows = (wtiles + G * chunk_wtiles - 1) / (G * chunk_wtiles);
+  (void)tiles;
+
+  auto chunk_first = [&](size_t w, size_t chunk) { return (w * G + chunk) * chunk_wtiles; };
+  auto load_tile = [&](vec16 (&r)[VPT], size_t wt, bool keep_in_l2) {
+    const size_t base = wt * WT;
+    if (base + WT <= n) {
+#pragma unroll
+      for (int v = 0; v < VPT; ++v) {
+        const char* p = reinterpret_cast<const char*>(in) + (base + (size_t)(v * 32 + lane) * VEC) * sizeof(T);
+#ifdef TB200_SCANW_EVICT_LAST
+        r[v] = keep_in_l2 ? load_l2_keep16(p, keep) : load_stream16(p);
+#else
+        r[v] = keep_in_l2 ? load_keep16<T>(p) : load_stream16(p);
+#endif
+      }
+    } else {
+#pragma unroll
+      for (int v = 0; v < VPT; ++v) {
+        T* e = reinterpret_cast<T*>(&r[v]);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+          const size_t i = base + (size_t)(v * 32 + lane) * VEC + k;
+          e[k] = i < n ? in[i] : ID;
+        }
+      }
+    }
+  };
+  // A: every warp reduces its part of the CTA's chunk of window w; the CTA's total is published
+  auto phase_a = [&](size_t w) {
+    const size_t first = chunk_first(w, c);
+    if (first >= wtiles) return;
+    const size_t mine = first + (size_t)warp * tiles_per_chunk;
+    T acc = ID;
+    for (unsigned t = 0; t < tiles_per_chunk; ++t) {
+      if (mine + t >= wtiles) break;
+      vec16 r[VPT];
+      load_tile(r, mine + t, true);
+#pragma unroll
+      for (int v = 0; v < VPT; ++v) {
+        const T* e = reinterpret_cast<const T*>(&r[v]);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) acc = op(acc, e[k]);
+      }
+    }
+    acc = warp_reduce_id(acc, op);
+    T* part = s_part[w & 1];
+    if (lane == 0) part[warp] = acc;
+    __syncthreads();
+    if (warp == 0) {
+      T t = lane < NWARPS ? part[lane] : ID;
+      t = warp_reduce_id(t, op);
+      if (lane == 0) ts.publish(w * G + c, TILE_AGGREGATE, t);
+    }
+  };
+
+  T running = has_init ? init : ID;   // init (+) everything before the current window
+  phase_a(0);
+  for (size_t w = 0; w < windows; ++w) {
+    if (w + 1 < windows) phase_a(w + 1);
+    const size_t first = chunk_first(w, c);
+    if (first >= wtiles) break;   // only in the last window: no chunk of this CTA, and nobody waits for it
+    // ---- F: fold the window's descriptors: every thread polls a few (all loads in flight at once),
+    // each warp leaves its partial fold in shared memory
+    {
+      constexpr int SLOTS = (int)(SCANW_MAX_GRID / SCAN_BLOCK);
+      T v[SLOTS];
+      unsigned st[SLOTS];
+#pragma unroll
+      for (int j = 0; j < SLOTS; ++j) {
+        const size_t k = threadIdx.x + (size_t)j * SCAN_BLOCK;
+        st[j] = TILE_AGGREGATE; v[j] = ID;
+        if (k < G && chunk_first(w, k) < wtiles) st[j] = ts.poll(w * G + k, v[j]);
+      }
+      T before = ID, total = ID;
+#pragma unroll
+      for (int j = 0; j < SLOTS; ++j) {
+        const size_t k = threadIdx.x + (size_t)j * SCAN_BLOCK;
+        unsigned iter = 0;
+        while (st[j] == TILE_INVALID) {
+          if (++iter > SPIN_LIMIT) { record_error(&hdr->error, ERR_LOOKBACK_TIMEOUT); v[j] = ID; break; }
+          backoff(iter);
+          st[j] = ts.poll(w * G + k, v[j]);
+        }
+        if (k < c) before = op(before, v[j]);
+        total = op(total, v[j]);
+      }
+      before = warp_reduce_id(before, op);
+      total = warp_reduce_id(total, op);
+      if (lane == 0) { s_fold[0][warp] = before; s_fold[1][warp] = total; }
+    }
+    __syncthreads();
+    // this warp's carry: init and the windows before, the chunks before this CTA's, the warps before this one
+    T carry;
+    {
+      T before = ID, total = ID;
+#pragma unroll
+      for (int w2 = 0; w2 < NWARPS; ++w2) { before = op(before, s_fold[0][w2]); total = op(total, s_fold[1][w2]); }
+      carry = op(running, before);
+      running = op(running, total);
+      const T* part = s_part[w & 1];
+#pragma unroll
+      for (int w2 = 0; w2 < NWARPS; ++w2) if (w2 < warp) carry = op(carry, part[w2]);
+    }
+    // ---- B: the warp scans its part of the chunk, tile after tile, no barrier
+    const size_t mine = first + (size_t)warp * tiles_per_chunk;
+#ifdef TB200_SCANW_PREFETCH
+    vec16 rn[VPT];
+    if (mine < wtiles) load_tile(rn, mine, false);
+#endif
+    for (unsigned t = 0; t < tiles_per_chunk; ++t) {
+      const size_t wt = mine + t;
+      if (wt >= wtiles) break;
+      vec16 r[VPT];
+#ifdef TB200_SCANW_PREFETCH
+#pragma unroll
+      for (int v = 0; v < VPT; ++v) r[v] = rn[v];
+      if (t + 1 < tiles_per_chunk && wt + 1 < wtiles) load_tile(rn, wt + 1, false);   // in flight while this tile is scanned
+#else
+      load_tile(r, wt, false);
+#endif
+      T x[VPT][VEC];
+#pragma unroll
+      for (int v = 0; v < VPT; ++v) {
+        const T* e = reinterpret_cast<const T*>(&r[v]);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) x[v][k] = e[k];
+      }
+      T pre[VPT];   // carry (+) everything of this tile before vector v of this lane
+      T rowacc = carry;
+#pragma unroll
+      for (int v = 0; v < VPT; ++v) {
+#pragma unroll
+        for (int k = 1; k < VEC; ++k) x[v][k] = op(x[v][k - 1], x[v][k]);
+        const T incl = warp_inclusive_scan(x[v][VEC - 1], op);
+        T lanepref = shfl_up(incl, 1);
+        if (lane == 0) lanepref = ID;
+        pre[v] = op(rowacc, lanepref);
+        rowacc = op(rowacc, shfl_idx(incl, 31));
+      }
+      carry = rowacc;
+      const size_t base = wt * WT;
+      const bool full = base + WT <= n;
+#pragma unroll
+      for (int v = 0; v < VPT; ++v) {
+        const T E = pre[v];
+        T y[VEC];
+        if (INCLUSIVE) {
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) y[k] = op(E, x[v][k]);
+        } else {
+          y[0] = E;
+#pragma unroll
+          for (int k = 1; k < VEC; ++k) y[k] = op(E, x[v][k - 1]);
+        }
+        const size_t i0 = base + (size_t)(v * 32 + lane) * VEC;
+        if (full) {
+          vec16 o;
+          T* e = reinterpret_cast<T*>(&o);
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) e[k] = y[k];
+          store_stream16(reinterpret_cast<char*>(out) + i0 * sizeof(T), o);
+        } else {
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) if (i0 + k < n) out[i0 + k] = y[k];
+        }
+      }
+    }
+    __syncthreads();   // s_fold is rewritten in the next window
+  }
+}
+
+// Resident CTAs of the windowed kernel on the current device (cached per kernel and device).
+template <class Kernel> int resident_ctas(Kernel kernel, int block, size_t smem) {
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, block, smem) != cudaSuccess || per_sm < 1) return 0;
+  return per_sm * current_device_info().sm_count;
+}
+
 template <class Op> struct is_commutative_op : std::false_type {};
 template <> struct is_commutative_op<plus_op> : std::true_type {};
 template <> struct is_commutative_op<min_op> : std::true_type {};
 template <> struct is_commutative_op<max_op> : std::true_type {};
 
 template <class T> size_t scan_tile_items() { return (size_t)SCAN_BLOCK * scan_tuning<T>::IPT; }
+// descriptors of the windowed route: one per chunk, the last window padded to a whole grid
+template <class T> size_t scanw_descriptor_bound(size_t n) {
+  const size_t tile = (size_t)SCAN_BLOCK * scan2_tuning<T>::IPT;
+  return ((n + tile - 1) / tile + TB200_SCANW_TPC - 1) / TB200_SCANW_TPC + SCANW_MAX_GRID;
+}
 template <class T> size_t scan_workspace_bytes(size_t n) {
   size_t tiles = (n + scan_tile_items<T>() - 1) / scan_tile_items<T>();
   const size_t single = tile_state<T>::bytes(tiles + 1), chunked = align_up(SCAN2_MAX_CHUNKS * sizeof(T), 256);
-  return sizeof(ws_header) + (single > chunked ? single : chunked);   // either route fits
+  size_t need = single > chunked ? single : chunked;
+  if (tile_state_mode<T>::value != 0 && tile_state<T>::bytes(scanw_descriptor_bound<T>(n)) > need) need = tile_state<T>::bytes(scanw_descriptor_bound<T>(n));
+  return sizeof(ws_header) + need;   // every route fits
 }
 
 // Launches the scan on `stream`; no sync.  in == out is allowed.
@@ -320,6 +591,28 @@ cudaError_t scan_async(InIt in, OutIt out, size_t n, T init, bool has_init, Op o
         const size_t tiles2 = (n + (size_t)SCAN_BLOCK * IPT2 - 1) / ((size_t)SCAN_BLOCK * IPT2);
         if (vectors && tiles2 >= SCAN2_MIN_TILES_PER_CHUNK * chunks) {
           constexpr int VEC = 16 / sizeof(T);
+#ifndef TB200_SCAN_NO_WINDOW
+          {
+            auto kern = scan_window_kernel<T, Op, INCLUSIVE, VEC, IPT2>;
+            static thread_local int resident[64] = {0};
+            int dev = 0;
+            cudaGetDevice(&dev);
+            if (dev >= 0 && dev < 64 && resident[dev] == 0) resident[dev] = resident_ctas(kern, SCAN_BLOCK, 0);
+            size_t grid = (dev >= 0 && dev < 64) ? (size_t)resident[dev] : 0;
+            if (grid > SCANW_MAX_GRID) grid = SCANW_MAX_GRID;
+            const unsigned tpc = TB200_SCANW_TPC;
+            if (grid > 0 && tiles2 >= 2 * grid * tpc) {
+              const size_t windows = (tiles2 + grid * tpc - 1) / (grid * tpc);
+              tile_state<T> tsw;
+              tsw.bind(base + sizeof(ws_header), windows * grid);
+              cudaError_t e3 = cudaMemsetAsync(base, 0, sizeof(ws_header) + tile_state<T>::bytes(windows * grid), stream);
+              if (e3 != cudaSuccess) return e3;
+              timed_launch tl(KID_SCAN, stream);
+              kern<<<(unsigned)grid, SCAN_BLOCK, 0, stream>>>(in, out, n, tiles2, tpc, init, has_init, op, tsw, hdr);
+              return cudaGetLastError();
+            }
+          }
+#endif
           const size_t tiles_per_chunk = (tiles2 + chunks - 1) / chunks;
           chunks = (tiles2 + tiles_per_chunk - 1) / tiles_per_chunk;
           T* partials = reinterpret_cast<T*>(base + sizeof(ws_header));

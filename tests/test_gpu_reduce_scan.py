@@ -109,6 +109,24 @@ def test_scan_fp32_tolerance(tb, port):
     assert np.max(np.abs(got - yard) / np.maximum(yard, 1.0)) < 1e-5
 
 
+@pytest.mark.parametrize("n", [(1 << 25) + 12345, 1 << 28])
+def test_scan_fp32_tolerance_on_the_large_input_route(tb, port, n):
+    """The fp32 variant of the benchmark configuration at the sizes that take the large-input route
+    (above a few million items): inclusive and exclusive plus-scan within 1e-5 relative of the
+    fp64-accumulated yardstick at EVERY position, in place as well."""
+    x = dg.scan_input_f32(n)
+    d = dev(x)
+    yard = port.scan_f32_via_f64(x).astype(np.float64)
+    got = host(tb.inclusive_scan(d)).astype(np.float64)
+    assert np.max(np.abs(got - yard) / np.maximum(yard, 1.0)) < 1e-5
+    del got
+    e = tb.exclusive_scan(d, 2.5)
+    tb.inclusive_scan(d, out=d)                                               # in place, testing/scan.cu:71-91
+    assert np.max(np.abs(host(d).astype(np.float64) - yard) / np.maximum(yard, 1.0)) < 1e-5
+    yard = port.scan_f32_via_f64(x, True, 2.5).astype(np.float64)
+    assert np.max(np.abs(host(e).astype(np.float64) - yard) / np.maximum(yard, 1.0)) < 1e-5
+
+
 def test_golden_reduce_scan(tb, golden):
     for n in (1, 777, 12345):
         assert tb.reduce(dev(golden[f"reduce_in_{n}"]), np.int64(0)) == golden[f"reduce_out_{n}"]

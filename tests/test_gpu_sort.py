@@ -146,3 +146,53 @@ def test_full_size_sort_properties(tb):
     ties = ki[1:] == ki[:-1]
     assert bool((vi[1:][ties] > vi[:-1][ties]).all())
     assert int(vi.long().sum()) == n * (n - 1) // 2
+
+
+def _sorted_permutation_stable(k0, k, v, as_signed_flip):
+    """k is sorted, k == k0[v] (v is the permutation applied) and v increases inside equal keys."""
+    if as_signed_flip is not None:                     # unsigned keys compared as signed integers
+        f = k ^ as_signed_flip
+        assert bool((f[1:] >= f[:-1]).all())
+    else:
+        assert bool((k[1:] >= k[:-1]).all())
+    assert torch.equal(k0[v.long()], k)
+    ties = k[1:] == k[:-1]
+    assert bool((v[1:][ties] > v[:-1][ties]).all())
+    n = k.numel()
+    assert int(v.long().sum()) == n * (n - 1) // 2
+
+
+def test_full_size_sort_u64_40bit_properties(tb):
+    """The second sort configuration at its size: 2^27 uint64 keys with 40 random bits (three digit
+    places are skipped on the device) and uint32 values = original index."""
+    n = 1 << 27
+    k0 = dev(dg.sort_keys_u64_40bit(n)).view(torch.int64)     # < 2^40: signed and unsigned order agree
+    k = k0.clone()
+    v = torch.arange(n, dtype=torch.int32, device="cuda")
+    tb.sort_by_key(k.view(torch.uint64), v.view(torch.uint32))
+    _sorted_permutation_stable(k0, k, v, None)
+
+
+def test_full_size_sort_u32_half_size_properties(tb):
+    n = 1 << 27
+    k0 = dev(dg.sort_keys_u32(n, seed=12)).view(torch.int32)
+    k = k0.clone()
+    v = torch.arange(n, dtype=torch.int32, device="cuda")
+    tb.sort_by_key(k.view(torch.uint32), v.view(torch.uint32))
+    _sorted_permutation_stable(k0, k, v, torch.tensor(-(1 << 31), dtype=torch.int32, device="cuda"))
+
+
+def test_full_size_stable_sort_zip_both_routes(tb):
+    """stable_sort of 2^26 zip(u32 key, float value) pairs by the key alone, on the comparison
+    (merge sort) route and on the radix route: each result sorted, a permutation, stable; the float
+    payload is the original index as a bit pattern, which must travel bit for bit."""
+    n = 1 << 26
+    k0 = dev(dg.zip_sort_input(n)[0] >> np.uint32(8)).view(torch.int32)      # 24-bit keys: plenty of ties
+    idx = torch.arange(n, dtype=torch.int32, device="cuda")
+    outs = []
+    for method in ("merge", "radix"):
+        k, v = k0.clone(), idx.clone()
+        tb.stable_sort_zip_by_first(k.view(torch.uint32), v.view(torch.float32), method=method)
+        _sorted_permutation_stable(k0, k, v, None)
+        outs.append((k, v))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])

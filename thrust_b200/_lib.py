@@ -38,6 +38,8 @@ PROTOTYPES = {
     "tb200_bucket_scatter": [_vp, _vp, _sz, _i, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _szp, _vp],
     "tb200_lower_bound": [_vp, _sz, _vp, _sz, _vp, _i, _i, _vp],
     "tb200_inclusive_scan_static": [_vp, _vp, _sz, _i, _i, _vp, _vp],
+    "tb200_inclusive_scan_static_limit": [_i, _szp],
+    "tb200_inclusive_scan_static_status": [_vp, C.POINTER(C.c_uint)],
     "tb200_ipc_export": [_vp, _vp, _szp],
     "tb200_ipc_open": [_vp, _sz, C.POINTER(C.c_void_p)],
     "tb200_ipc_close_all": [],

@@ -7,6 +7,8 @@
 // is fully committed to its own data.  For them this one entry point carries its own scratch: a
 // fixed array in the library's device data segment, present on every GPU that loads the library
 // from the moment it is loaded until the process exits.
+#include <atomic>
+
 #include "abi_common.cuh"
 #include "thrust_b200/scan.cuh"
 
@@ -14,25 +16,36 @@ using namespace tb200_abi;
 
 namespace {
 
-// 256 KiB: the tile descriptors of up to about 2^28 four-byte elements or 2^25 eight-byte elements.
-constexpr size_t STATIC_SCRATCH_BYTES = 256 * 1024;
+// 512 KiB: the descriptors of up to 536,600,576 four-byte or 134,148,096 eight-byte elements (the
+// exact figure follows the kernels' tile sizes; tb200_inclusive_scan_static_limit reports it).
+constexpr size_t STATIC_SCRATCH_BYTES = 512 * 1024;
 static __device__ __align__(256) unsigned char g_scan_scratch[STATIC_SCRATCH_BYTES];
 
 // In host code the name g_scan_scratch is only a handle for the runtime, not a device address, so
 // the address is looked up once per device (with that device current) and remembered.
+// (Threads that race on a device's first call each look the address up and store the same value.)
 void* scratch_address(cudaError_t& err) {
-  static void* per_device[64] = {nullptr};
+  static std::atomic<void*> per_device[64];
   int dev = 0;
   err = cudaGetDevice(&dev);
   if (err != cudaSuccess) return nullptr;
   if (dev < 0 || dev >= 64) { err = cudaErrorInvalidDevice; return nullptr; }
-  if (!per_device[dev]) {
-    void* p = nullptr;
+  void* p = per_device[dev].load(std::memory_order_acquire);
+  if (!p) {
     err = cudaGetSymbolAddress(&p, g_scan_scratch);
     if (err != cudaSuccess) return nullptr;
-    per_device[dev] = p;
+    per_device[dev].store(p, std::memory_order_release);
   }
-  return per_device[dev];
+  return p;
+}
+
+template <class T> size_t largest_n() {
+  size_t lo = 0, hi = (size_t)1 << 40;   // scan_workspace_bytes grows with n
+  while (lo < hi) {
+    const size_t mid = lo + (hi - lo + 1) / 2;
+    if (tb200::scan_workspace_bytes<T>(mid) <= STATIC_SCRATCH_BYTES) lo = mid; else hi = mid - 1;
+  }
+  return lo;
 }
 
 }  // namespace
@@ -54,4 +67,23 @@ TB200_API int tb200_inclusive_scan_static(const void* d_in, void* d_out, size_t 
       return (int)tb200::scan_async<true>(static_cast<const T*>(d_in), static_cast<T*>(d_out), n, init, has_init, o, ws, stream);
     });
   });
+}
+
+TB200_API int tb200_inclusive_scan_static_limit(int t, size_t* h_max_n) {
+  if (!h_max_n) return ERR_INVALID;
+  return by_wide_dtype(t, [&](auto tv) -> int {
+    *h_max_n = largest_n<decltype(tv)>();
+    return 0;
+  });
+}
+
+TB200_API int tb200_inclusive_scan_static_status(tb200_stream_t stream, unsigned* h_status) {
+  if (!h_status) return ERR_INVALID;
+  cudaError_t err = cudaSuccess;
+  void* ws = scratch_address(err);
+  if (!ws) return (int)err;
+  // the array begins with the same header as a caller's workspace: its first word is the status
+  err = cudaMemcpyAsync(h_status, ws, sizeof(unsigned), cudaMemcpyDeviceToHost, stream);
+  if (err != cudaSuccess) return (int)err;
+  return (int)cudaStreamSynchronize(stream);
 }
