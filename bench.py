@@ -17,8 +17,9 @@ value = original index).  Rank 0 prints ONE JSON line:
   others       the remaining hot-path algorithms at their benchmark sizes (N=1 only).
 
 With N > 1 (torchrun, one rank per GPU) the same 2^28 pairs are split across the ranks and sorted
-by thrust_b200.sharded.sharded_sort_by_key: sampled splitters, one scatter kernel per GPU that stores
-each pair into its owner's receive buffer over NVLink (CUDA IPC), then a stable per-GPU radix sort ("scaling": "strong").  `--impl reference` times the
+by thrust_b200.sharded.sharded_sort_by_key: splitters from an all-gathered digit histogram, one scatter
+kernel per GPU that stores each pair into its owner's receive buffer over NVLink (CUDA IPC), then a
+stable per-GPU radix sort ("scaling": "strong"); the sharded result is verified after the timed steps.  `--impl reference` times the
 reference's own CPU implementation (OpenMP backend) on the host cores instead.
 """
 import argparse
@@ -130,6 +131,12 @@ def run_reference(args):
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": o.threads, "kind": o.kind, "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
+
+
+def _mark(torch):
+    e = torch.cuda.Event(enable_timing=True)
+    e.record()
+    return e
 
 
 def _events(torch):
@@ -364,8 +371,8 @@ def run_ours(args):
         def step():
             # like thrust::sort_by_key, the sharded sort may consume its input
             out["k"], out["v"] = sharded.sharded_sort_by_key(k, v, consume_input=True)
-        # per rank: sample sort (7) + bucket count (1) + bucket scatter (1) + local sort (7)
-        launches_per_step = 7 + 1 + 1 + 7
+        # per rank: digit histogram (1) + plan (1) + scatter (1) + local sort (histogram, bases, four passes, copy-back check: 7)
+        launches_per_step = 1 + 1 + 1 + 7
 
     # the clock sampler runs from before the warm-up to after the timed steps, so that even a timed
     # region of a few tens of milliseconds is covered by samples taken under the same load
@@ -400,6 +407,20 @@ def run_ours(args):
         ki = k.view(torch.int32) ^ torch.tensor(-(1 << 31), dtype=torch.int32, device="cuda")
         assert bool((ki[1:] >= ki[:-1]).all()), "output is not sorted"
         del ki
+    verified = None
+    stages = None
+    if world > 1:
+        # the whole sharded result: genuine pairs, sorted and stable inside every shard, shards in
+        # rank order, values a permutation of 0 .. n-1 (thrust_b200.sharded.check_sharded_sort)
+        verified = sharded.check_sharded_sort(out["k"], out["v"], N_KEYS, dg.sort_keys_u32_at)
+        # where a step's time goes: CUDA events at the stage boundaries of one more step
+        marks = [("start", lambda: _mark(torch))]
+        restore()
+        marks.append(("begin", _mark(torch)))
+        sharded.sharded_sort_by_key(k, v, consume_input=True, stage_marks=marks)
+        torch.cuda.synchronize()
+        evs = marks[1:]
+        stages = {evs[i + 1][0] + "_ms": evs[i][1].elapsed_time(evs[i + 1][1]) for i in range(len(evs) - 1)}
 
     # ---- roofline of the dominant kernel: one onesweep digit pass, timed with the library's events
     lib.tb200_kernel_timing(1)
@@ -458,9 +479,9 @@ def run_ours(args):
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u32", "data": "synthetic",
         "config": {"workload": WORKLOAD, "n": N_KEYS, "per_gpu": n_local,
                    "l2": "2 GiB of input per step (> 126 MB L2); the pristine input is restored by a 2 GiB device copy between timed steps",
-                   "parallelism": "1 GPU" if world == 1 else "%d GPUs: sampled splitters, one scatter kernel per GPU storing each pair into the owning GPU's receive buffer over NVLink (CUDA IPC), local radix sort of what arrived" % world},
+                   "parallelism": "1 GPU" if world == 1 else "%d GPUs: splitters from an all-gathered 12-bit digit histogram, one scatter kernel per GPU storing each pair into the owning GPU's receive buffer over NVLink (CUDA IPC), local radix sort of what arrived" % world},
         "roofline": roofline, "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
-        "wall_s_timed_region": t_wall,
+        "wall_s_timed_region": t_wall, "verified": verified, "stages_ms": stages,
         "sort_roofline": {"algorithmic_bytes_per_key": 68, "achieved_gbs": 68.0 * N_KEYS / ms / 1e6, "frac_of_hbm_peak": 68.0 * N_KEYS / ms / 1e6 / peak / world},
     }
 
@@ -497,6 +518,9 @@ def main():
     ap.add_argument("--no-extras", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
+        # a launcher may have pinned OpenMP to one thread for its ranks; the reference arm runs on rank 0
+        # alone and is meant to use every host core (read when the oracle library loads its OpenMP runtime)
+        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
         run_reference(args)
     else:
         run_ours(args)

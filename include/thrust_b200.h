@@ -249,6 +249,32 @@ int tb200_bucket_scatter(const void* d_keys, const void* d_vals, size_t n, int k
                          const unsigned long long* h_dst_offsets, void* d_ws, size_t* ws_bytes,
                          tb200_stream_t stream);
 
+/* The same exchange with splitters taken from a digit histogram instead of a sorted sample: no
+ * second pass over the keys, one collective, no sampling error.  No counterpart in the reference.
+ *   tb200_exchange_sizes   words of one rank's histogram row, bytes of a plan, and bytes of the plan's
+ *                          head (what a host needs to read back: field, ranks, send_offset[16],
+ *                          recv_total[16], tag[16], 8 bytes each after two 4-byte words);
+ *   tb200_exchange_hist    d_row = histograms of the 12-bit fields of the keys' order-preserving
+ *                          codes (I32/U32/F32: the top field; 64-bit keys: the four top fields),
+ *                          followed by `tag` and n; all-gather the rows of all ranks (rank order);
+ *   tb200_exchange_plan    from the gathered rows, identically on every rank: the highest field in
+ *                          which the keys differ partitions them, contiguous bin ranges go to the
+ *                          ranks in order, balanced to one bin's size; this rank's offsets into every
+ *                          receive buffer (source-rank-major) and every rank's receive total;
+ *   tb200_exchange_scatter one kernel: every pair stored straight into the receive buffer of the
+ *                          rank that owns its bin (h_dst_keys[r] / h_dst_vals[r], local or opened
+ *                          with tb200_ipc_open), in input order inside a source (stable).
+ * ranks <= 16, n < 2^30 per rank.  Receivers must not touch their buffers until every sender's
+ * scatter has completed (order with a collective); a stable local sort of what arrived finishes. */
+int tb200_exchange_sizes(int key_t, size_t* h_row_words, size_t* h_plan_bytes, size_t* h_plan_head_bytes);
+int tb200_exchange_hist(const void* d_keys, size_t n, int key_t, int descending, unsigned long long tag,
+                        unsigned* d_row, tb200_stream_t stream);
+int tb200_exchange_plan(const unsigned* d_rows, int ranks, int rank, int key_t, void* d_plan,
+                        tb200_stream_t stream);
+int tb200_exchange_scatter(const void* d_keys, const void* d_vals, size_t n, int key_t, int val_bytes,
+                           int descending, const void* d_plan, int ranks, void* const* h_dst_keys,
+                           void* const* h_dst_vals, void* d_ws, size_t* ws_bytes, tb200_stream_t stream);
+
 /* Sharing device buffers between the ranks of a one-process-per-GPU job, so that a kernel on one
  * GPU reads another GPU's buffer directly over NVLink with ordinary loads (the multi-GPU sort
  * merges the runs it needs straight out of its peers' memory instead of copying them first).

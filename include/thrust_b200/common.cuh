@@ -8,7 +8,10 @@
 #include <stdint.h>
 #include <stddef.h>
 #include <type_traits>
+#include <new>
 #include <string.h>
+#include <stdio.h>
+#include <stdlib.h>
 
 namespace tb200 {
 
@@ -25,6 +28,15 @@ constexpr int WARP_THREADS = 32;
 
 constexpr unsigned FULL_MASK = 0xffffffffu;
 
+// Stores a value into a slot of such raw storage: plain assignment for trivially copyable types, copy
+// construction in place otherwise -- assigning to memory in which no object was ever constructed is
+// wrong for a type with a non-trivial assignment operator (the reference guards this case:
+// testing/copy.cu:470-520).
+template <class T> __device__ __forceinline__ void stash(T* slot, const T& v) {
+  if constexpr (std::is_trivially_copyable<T>::value) *slot = v;
+  else ::new (static_cast<void*>(slot)) T(v);
+}
+
 // Error codes a kernel may leave in the workspace status word (see ws_header).
 enum : unsigned { ERR_NONE = 0, ERR_LOOKBACK_TIMEOUT = 1 };
 
@@ -32,7 +44,10 @@ enum : unsigned { ERR_NONE = 0, ERR_LOOKBACK_TIMEOUT = 1 };
 // ERR_LOOKBACK_TIMEOUT and carries on with whatever it has.  Polls past the first few sleep
 // ~100 ns, so the bound is of the order of a second: far beyond any legitimate wait, short
 // enough that a broken launch returns instead of hanging the device.
-constexpr unsigned SPIN_LIMIT = 1u << 23;
+#ifndef TB200_SPIN_LIMIT
+#define TB200_SPIN_LIMIT (1u << 23)
+#endif
+constexpr unsigned SPIN_LIMIT = TB200_SPIN_LIMIT;   // a test build of the library shortens it to make a wait run out
 
 // First 256 bytes of every workspace.
 struct ws_header {
@@ -45,18 +60,30 @@ struct ws_header {
 };
 static_assert(sizeof(ws_header) == 256, "workspace header is 256 bytes");
 
+#ifdef TB200_TEST_HOOKS
+// Test build of the library only: a process-wide switch that the single-pass scan copies into the
+// workspace header's flags (bit 0: tile 0 does not publish).
+inline unsigned& test_hook_flags() { static unsigned f = 0; return f; }
+#endif
+
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
+// Properties of the current device, looked up once per host thread and device.  If the runtime
+// cannot answer (no device, a failed context) the fallback describes a B200 and is NOT cached: the
+// launch that follows reports the real error.
 struct device_info { int sm_count; int max_smem_optin; };
 inline const device_info& current_device_info() {
   static thread_local device_info cache[64];
   static thread_local bool have[64] = {false};
+  static const device_info fallback = {148, 232448};
   int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fallback;
   if (!have[dev]) {
-    cudaDeviceGetAttribute(&cache[dev].sm_count, cudaDevAttrMultiProcessorCount, dev);
-    cudaDeviceGetAttribute(&cache[dev].max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    device_info di;
+    if (cudaDeviceGetAttribute(&di.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&di.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess || di.sm_count < 1)
+      return fallback;
+    cache[dev] = di;
     have[dev] = true;
   }
   return cache[dev];
@@ -94,6 +121,21 @@ struct timed_launch {
   timed_launch(int id, cudaStream_t stream) : slot(global_kernel_timer().begin(id, stream)), s(stream) {}
   ~timed_launch() { global_kernel_timer().end(slot, s); }
 };
+
+// Launch log, the analogue of the reference's THRUST_DEBUG_SYNC trace
+// (thrust/system/cuda/detail/core/agent_launcher.h:518-590): with THRUST_B200_LOG=1 in the
+// environment every dominant kernel launch prints one line to stderr -- kernel, grid, block, dynamic
+// shared memory, items -- and, like the reference's debug mode, waits for the stream and reports the
+// launch's status.  Off (one cached flag test) otherwise.
+inline bool launch_log_enabled() {
+  static const bool on = [] { const char* e = getenv("THRUST_B200_LOG"); return e && e[0] && e[0] != '0'; }();
+  return on;
+}
+inline void log_launch(const char* kernel, size_t grid, int block, size_t smem, size_t items, cudaStream_t stream) {
+  if (!launch_log_enabled()) return;
+  const cudaError_t e = cudaStreamSynchronize(stream);
+  fprintf(stderr, "thrust_b200: %s<<<%zu, %d, %zu>>> items=%zu status=%s\n", kernel, grid, block, smem, items, cudaGetErrorName(e));
+}
 
 // ---------------------------------------------------------------- functors
 struct plus_op { template <class T> __host__ __device__ T operator()(const T& a, const T& b) const { return a + b; } };
@@ -278,6 +320,30 @@ __device__ __forceinline__ void st_relaxed_u32(unsigned* p, unsigned v) {
   asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+// L2-coherent load of any trivially copyable value (what another CTA of the same grid has just
+// written, after a __threadfence on both sides): built-in 4- and 8-byte words where the size allows,
+// bytes otherwise, so that structs and tuples work like scalars.
+template <class T> __device__ __forceinline__ T load_cg_any(const T* p) {
+  T v;
+  if constexpr (sizeof(T) % 8 == 0 && alignof(T) >= 8) {
+    unsigned long long w[sizeof(T) / 8];
+#pragma unroll
+    for (int q = 0; q < (int)(sizeof(T) / 8); ++q) w[q] = __ldcg(reinterpret_cast<const unsigned long long*>(p) + q);
+    memcpy(&v, w, sizeof(T));
+  } else if constexpr (sizeof(T) % 4 == 0 && alignof(T) >= 4) {
+    unsigned w[sizeof(T) / 4];
+#pragma unroll
+    for (int q = 0; q < (int)(sizeof(T) / 4); ++q) w[q] = __ldcg(reinterpret_cast<const unsigned*>(p) + q);
+    memcpy(&v, w, sizeof(T));
+  } else {
+    unsigned char w[sizeof(T)];
+#pragma unroll
+    for (int q = 0; q < (int)sizeof(T); ++q) w[q] = __ldcg(reinterpret_cast<const unsigned char*>(p) + q);
+    memcpy(&v, w, sizeof(T));
+  }
+  return v;
+}
+
 __device__ __forceinline__ void record_error(unsigned* err, unsigned code) { atomicCAS(err, ERR_NONE, code); }
 
 __device__ __forceinline__ void backoff(unsigned iter) { if (iter > 8) __nanosleep(iter > 64 ? 200 : 40); }
@@ -442,6 +508,11 @@ __device__ __forceinline__ void tile_exclusive_prefix(const T (&vec_total)[VPT],
     if (tile == 0) {
       T inc = has_init ? op(init, agg) : agg;
       if (lane == 0) {
+#ifdef TB200_TEST_HOOKS
+        // test build only: with bit 0 of the header's flags set, tile 0 never publishes, so that its
+        // successors' bounded waits run out (err points at the header's first word)
+        if ((reinterpret_cast<const ws_header*>(err)->flags & 1u) == 0)
+#endif
         ts.publish(0, TILE_INCLUSIVE, inc);
         sm.prefix = init; sm.has_prefix = has_init; sm.inclusive = inc;
       }

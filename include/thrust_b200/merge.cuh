@@ -21,8 +21,15 @@ namespace tb200 {
 
 constexpr int MERGE_BLOCK = 256;
 
+// Items per thread: tuned for the small types, then whatever keeps the staged tile (keys and
+// payloads of 256 * IPT items) inside 44 KB of static shared memory, as the reference sizes its
+// tiles by sizeof(T) (thrust/system/cuda/detail/merge.h:301-360).
+constexpr int MERGE_SMEM_BUDGET = 44 * 1024;
 template <int KB, int VB> struct merge_tuning {
-  static constexpr int IPT = (KB + VB) <= 8 ? 15 : ((KB + VB) <= 12 ? 11 : 9);
+  static constexpr int TUNED = (KB + VB) <= 8 ? 15 : ((KB + VB) <= 12 ? 11 : 9);
+  static constexpr int FIT = MERGE_SMEM_BUDGET / (MERGE_BLOCK * (KB + VB));
+  static constexpr int IPT = TUNED < FIT ? TUNED : (FIT < 1 ? 1 : FIT);
+  static_assert(MERGE_BLOCK * IPT * (KB + VB) + KB <= 48 * 1024, "key + payload too large for the merge tile (more than 160 bytes per item)");
 };
 
 // Number of items taken from A among the first `diag` outputs of merge(A[0,na), B[0,nb)).
@@ -109,7 +116,7 @@ merge_kernel(KeyItA ka, KeyItB kb, ValItA va, ValItB vb, KeyOutIt ko, ValOutIt v
 #pragma unroll
   for (int i = 0; i < IPT; ++i) {
     unsigned c = threadIdx.x + i * MERGE_BLOCK;
-    if (c < tile_n) s_key[c] = c < na ? (K)ka[a_begin + c] : (K)kb[b_begin + (c - na)];
+    if (c < tile_n) stash(&s_key[c], c < na ? (K)ka[a_begin + c] : (K)kb[b_begin + (c - na)]);
   }
   __syncthreads();
 
@@ -131,7 +138,7 @@ merge_kernel(KeyItA ka, KeyItB kb, ValItA va, ValItB vb, KeyOutIt ko, ValOutIt v
   __syncthreads();
   // ---- keys out through shared memory (thread's outputs are consecutive; stores become coalesced)
 #pragma unroll
-  for (int i = 0; i < IPT; ++i) { unsigned j = threadIdx.x * IPT + i; if (j < tile_n) s_key[j] = out_k[i]; }
+  for (int i = 0; i < IPT; ++i) { unsigned j = threadIdx.x * IPT + i; if (j < tile_n) stash(&s_key[j], out_k[i]); }
   __syncthreads();
 #pragma unroll
   for (int i = 0; i < IPT; ++i) { unsigned c = threadIdx.x + i * MERGE_BLOCK; if (c < tile_n) ko[out0 + c] = s_key[c]; }
@@ -144,14 +151,14 @@ merge_kernel(KeyItA ka, KeyItB kb, ValItA va, ValItB vb, KeyOutIt ko, ValOutIt v
       if (c < tile_n) v_in[i] = c < na ? (V)va[a_begin + c] : (V)vb[b_begin + (c - na)];
     }
 #pragma unroll
-    for (int i = 0; i < IPT; ++i) { unsigned c = threadIdx.x + i * MERGE_BLOCK; if (c < tile_n) s_val[c] = v_in[i]; }
+    for (int i = 0; i < IPT; ++i) { unsigned c = threadIdx.x + i * MERGE_BLOCK; if (c < tile_n) stash(&s_val[c], v_in[i]); }
     __syncthreads();
     V out_v[IPT];
 #pragma unroll
     for (int i = 0; i < IPT; ++i) { unsigned j = threadIdx.x * IPT + i; if (j < tile_n) out_v[i] = s_val[src[i]]; }
     __syncthreads();
 #pragma unroll
-    for (int i = 0; i < IPT; ++i) { unsigned j = threadIdx.x * IPT + i; if (j < tile_n) s_val[j] = out_v[i]; }
+    for (int i = 0; i < IPT; ++i) { unsigned j = threadIdx.x * IPT + i; if (j < tile_n) stash(&s_val[j], out_v[i]); }
     __syncthreads();
 #pragma unroll
     for (int i = 0; i < IPT; ++i) { unsigned c = threadIdx.x + i * MERGE_BLOCK; if (c < tile_n) vo[out0 + c] = s_val[c]; }
@@ -195,7 +202,10 @@ cudaError_t merge_async(KeyItA ka, size_t na, KeyItB kb, size_t nb, ValItA va, V
 
 // ---------------------------------------------------------------- merge sort
 template <int KB, int VB> struct block_sort_tuning {
-  static constexpr int IPT = (KB + VB) <= 8 ? 16 : 8;   // power-of-two friendly tile: 256 * IPT items
+  // power-of-two friendly tile of 256 * IPT items whose keys (+ a 2-byte index each) fit 44 KB of shared memory
+  static constexpr int FIT = MERGE_SMEM_BUDGET / (MERGE_BLOCK * (KB + 2));
+  static constexpr int IPT = (KB + VB) <= 8 ? 16 : (FIT >= 8 ? 8 : FIT >= 4 ? 4 : FIT >= 2 ? 2 : 1);
+  static_assert(MERGE_BLOCK * IPT * (KB + 2) + KB + 2 <= 48 * 1024, "key too large for the block sort tile (more than 170 bytes)");
 };
 
 template <class KeyIt, class ValIt, class KeyOutIt, class ValOutIt, class K, class V, bool HAS_V, class Comp, int IPT>
@@ -209,7 +219,7 @@ block_sort_kernel(KeyIt keys, ValIt vals, KeyOutIt keys_out, ValOutIt vals_out, 
 
   // ---- coalesced load, then each thread takes IPT consecutive items
 #pragma unroll
-  for (int i = 0; i < IPT; ++i) { unsigned c = threadIdx.x + i * MERGE_BLOCK; if (c < tile_n) s_key[c] = keys[base + c]; }
+  for (int i = 0; i < IPT; ++i) { unsigned c = threadIdx.x + i * MERGE_BLOCK; if (c < tile_n) stash(&s_key[c], (K)keys[base + c]); }
   __syncthreads();
   K k[IPT]; unsigned short idx[IPT];
   const unsigned first = threadIdx.x * IPT;
@@ -239,7 +249,7 @@ block_sort_kernel(KeyIt keys, ValIt vals, KeyOutIt keys_out, ValOutIt vals_out, 
   for (unsigned len = IPT; len < (unsigned)TILE; len <<= 1) {
     __syncthreads();
 #pragma unroll
-    for (int i = 0; i < IPT; ++i) { s_key[first + i] = k[i]; s_idx[first + i] = idx[i]; }
+    for (int i = 0; i < IPT; ++i) { stash(&s_key[first + i], k[i]); s_idx[first + i] = idx[i]; }
     __syncthreads();
     const unsigned pair0 = first / (2 * len) * (2 * len);
     const unsigned a0 = pair0, b0 = pair0 + len;
@@ -264,7 +274,7 @@ block_sort_kernel(KeyIt keys, ValIt vals, KeyOutIt keys_out, ValOutIt vals_out, 
   }
   __syncthreads();
 #pragma unroll
-  for (int i = 0; i < IPT; ++i) { s_key[first + i] = k[i]; s_idx[first + i] = idx[i]; }
+  for (int i = 0; i < IPT; ++i) { stash(&s_key[first + i], k[i]); s_idx[first + i] = idx[i]; }
   __syncthreads();
   // gather the payloads by source index before anything is written: the output may be the input
   V v_out[HAS_V ? IPT : 1];

@@ -558,6 +558,166 @@ bucket_scatter_kernel(const UK* src, const UV* vsrc, unsigned n, key_coding codi
   sweep_tiles<UK, UV, HAS_V, Policy, LB, IPT>(src, vsrc, n, &hdr->ticket, policy, my_bin_base, lookback, &hdr->error, smem_raw);
 }
 
+// ---------------------------------------------------------------- multi-GPU: splitters from a digit histogram
+// The exchange of the multi-GPU sort without sampling: every GPU histograms a 12-bit field of its
+// keys' order-preserving codes (one read of the keys), the histograms are all-gathered (ONE
+// collective), and every GPU derives the same plan from them: which bins go to which GPU (contiguous
+// bin ranges, balanced to one bin's size), where its own items start in each destination's receive
+// buffer (source-rank-major, which keeps the exchange stable) and how much every GPU receives.
+// 32-bit keys use their top 12 bits; 64-bit keys offer their four top 12-bit fields and the plan
+// takes the highest one in which the keys differ (all fields above it are then equal in every key,
+// so that field alone orders the bins).  Heavily skewed keys make unequal shares; the caller reads
+// the shares and may fall back to sampled splitters.
+constexpr int EXCH_BITS = 12;
+constexpr int EXCH_BINS = 1 << EXCH_BITS;
+constexpr int EXCH_MAX_FIELDS = 4;
+constexpr int EXCH_ROW_TAIL = 4;   // words behind a rank's histograms: a caller's tag (2 words), its item count (2 words)
+template <class UK> constexpr int exch_fields() { return sizeof(UK) == 8 ? 4 : 1; }
+template <class UK> __host__ __device__ constexpr int exch_shift(int field) { return 8 * (int)sizeof(UK) - EXCH_BITS * (field + 1); }
+inline size_t exch_row_words(int fields) { return (size_t)fields * EXCH_BINS + EXCH_ROW_TAIL; }
+
+struct exchange_plan {
+  unsigned field;                                  // which 12-bit field partitions the keys
+  unsigned ranks;
+  unsigned long long send_offset[MAX_BUCKETS];     // where this rank's items start in destination d's receive buffer
+  unsigned long long recv_total[MAX_BUCKETS];      // items destination d receives in all
+  unsigned long long tag[MAX_BUCKETS];             // the tag each rank handed to its histogram call
+  unsigned char lut[EXCH_BINS];                    // bin -> destination
+};
+
+template <class UK>
+__global__ void __launch_bounds__(1024)
+exchange_hist_kernel(const UK* keys, size_t n, key_coding coding, unsigned long long tag, unsigned* row) {
+  constexpr int F = exch_fields<UK>();
+  extern __shared__ __align__(16) unsigned exch_bins[];   // [F][4096]
+  for (int i = threadIdx.x; i < F * EXCH_BINS; i += 1024) exch_bins[i] = 0;
+  __syncthreads();
+  const size_t stride = (size_t)gridDim.x * 1024;
+  constexpr int U = 4;
+  size_t i = (size_t)blockIdx.x * 1024 + threadIdx.x;
+  auto account = [&](UK k) {
+    const UK c = key_code(k, coding);
+#pragma unroll
+    for (int f = 0; f < F; ++f) atomicAdd(&exch_bins[f * EXCH_BINS + ((unsigned)(c >> exch_shift<UK>(f)) & (EXCH_BINS - 1))], 1u);
+  };
+  for (; i + (U - 1) * stride < n; i += U * stride) {
+    UK k[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) k[u] = __ldcs(keys + i + u * stride);
+#pragma unroll
+    for (int u = 0; u < U; ++u) account(k[u]);
+  }
+  for (; i < n; i += stride) account(__ldcs(keys + i));
+  __syncthreads();
+  for (int j = threadIdx.x; j < F * EXCH_BINS; j += 1024) {
+    const unsigned c = exch_bins[j];
+    if (c) atomicAdd(&row[j], c);
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    unsigned* tail = row + F * EXCH_BINS;
+    tail[0] = (unsigned)tag; tail[1] = (unsigned)(tag >> 32);
+    tail[2] = (unsigned)n; tail[3] = (unsigned)((unsigned long long)n >> 32);
+  }
+}
+
+// One CTA.  rows: [ranks][fields * 4096 + EXCH_ROW_TAIL] words, the all-gathered histograms.
+template <int UNUSED = 0>
+__global__ void __launch_bounds__(1024)
+exchange_plan_kernel(const unsigned* rows, int ranks, int rank, int fields, exchange_plan* plan) {
+  __shared__ unsigned long long s_total[EXCH_BINS];
+  __shared__ unsigned long long s_cnt[MAX_BUCKETS][MAX_BUCKETS];   // [source][destination]
+  __shared__ unsigned long long s_warp[32];
+  __shared__ unsigned char s_dest[EXCH_BINS];
+  const size_t row_words = (size_t)fields * EXCH_BINS + EXCH_ROW_TAIL;
+  const int lane = lane_id(), warp = threadIdx.x >> 5;
+  // the highest field in which the keys differ (a field whose every key shares one bin is skipped)
+  int field = 0;
+  for (; field < fields; ++field) {
+    int nonzero = 0;
+    for (int b = threadIdx.x; b < EXCH_BINS; b += 1024) {
+      unsigned long long t = 0;
+      for (int g = 0; g < ranks; ++g) t += rows[(size_t)g * row_words + (size_t)field * EXCH_BINS + b];
+      s_total[b] = t;
+      nonzero += t != 0;
+    }
+    int used = nonzero;
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) used += __shfl_xor_sync(FULL_MASK, used, d);
+    if (lane == 0) s_warp[warp] = (unsigned long long)used;
+    __syncthreads();
+    unsigned long long all_used = 0;
+    for (int w = 0; w < 32; ++w) all_used += s_warp[w];
+    __syncthreads();
+    if (all_used > 1 || field == fields - 1) break;
+  }
+  // exclusive prefix of the bins: thread t owns bins 4t .. 4t+3
+  unsigned long long mine[4], sum = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) { mine[j] = sum; sum += s_total[threadIdx.x * 4 + j]; }
+  unsigned long long incl = warp_inclusive_scan(sum, plus_op());
+  if (lane == 31) s_warp[warp] = incl;
+  for (int i = threadIdx.x; i < MAX_BUCKETS * MAX_BUCKETS; i += 1024) (&s_cnt[0][0])[i] = 0;
+  __syncthreads();
+  unsigned long long before = incl - sum, n_all = 0;
+  for (int w = 0; w < 32; ++w) { if (w < warp) before += s_warp[w]; n_all += s_warp[w]; }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int b = threadIdx.x * 4 + j;
+    unsigned long long d = n_all ? (before + mine[j]) * (unsigned long long)ranks / n_all : 0;   // the share in which the bin starts
+    if (d > (unsigned long long)(ranks - 1)) d = ranks - 1;
+    s_dest[b] = (unsigned char)d;
+    plan->lut[b] = (unsigned char)d;
+    for (int g = 0; g < ranks; ++g) {
+      const unsigned c = rows[(size_t)g * row_words + (size_t)field * EXCH_BINS + b];
+      if (c) atomicAdd(&s_cnt[g][d], (unsigned long long)c);
+    }
+  }
+  __syncthreads();
+  if ((int)threadIdx.x < ranks) {
+    const int d = threadIdx.x;
+    unsigned long long off = 0, total = 0;
+    for (int g = 0; g < ranks; ++g) { if (g < rank) off += s_cnt[g][d]; total += s_cnt[g][d]; }
+    plan->send_offset[d] = off;
+    plan->recv_total[d] = total;
+    const unsigned* tail = rows + (size_t)d * row_words + (size_t)fields * EXCH_BINS;
+    plan->tag[d] = (unsigned long long)tail[0] | ((unsigned long long)tail[1] << 32);
+  }
+  if (threadIdx.x == 0) { plan->field = (unsigned)field; plan->ranks = (unsigned)ranks; }
+}
+
+// bin of a key = plan->lut[its field]; bin b goes to destination b, possibly a buffer in another
+// GPU's memory (ordinary stores over NVLink)
+template <class UK, class UV> struct exchange_policy {
+  static constexpr int BITS = 4;
+  static constexpr int MATCH_EVERY = 0;
+  key_coding coding; int shift;
+  const unsigned char* lut;              // shared memory, 4096 entries
+  UK* const* dst_k; UV* const* dst_v;    // shared memory tables of destination pointers
+  __device__ __forceinline__ unsigned digit(UK k) const { return lut[(unsigned)(key_code(k, coding) >> shift) & (EXCH_BINS - 1)]; }
+  __device__ __forceinline__ UK* keys_of(unsigned d) const { return dst_k[d]; }
+  __device__ __forceinline__ UV* vals_of(unsigned d) const { return dst_v[d]; }
+};
+
+template <class UK, class UV, bool HAS_V, class LB, int IPT>
+__global__ void __launch_bounds__(ONESWEEP_BLOCK, ONESWEEP_CTAS_PER_SM)
+exchange_scatter_kernel(const UK* src, const UV* vsrc, unsigned n, key_coding coding, const exchange_plan* plan, bucket_table<UK, UV> table,
+                        LB* lookback, ws_header* hdr) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ unsigned char s_lut[EXCH_BINS];
+  __shared__ UK* s_dst_k[MAX_BUCKETS];
+  __shared__ UV* s_dst_v[MAX_BUCKETS];
+  for (int i = threadIdx.x; i < EXCH_BINS / 4; i += ONESWEEP_BLOCK) reinterpret_cast<unsigned*>(s_lut)[i] = reinterpret_cast<const unsigned*>(plan->lut)[i];
+  if (threadIdx.x < MAX_BUCKETS) {
+    s_dst_k[threadIdx.x] = table.dst_k[threadIdx.x];
+    s_dst_v[threadIdx.x] = table.dst_v[threadIdx.x];
+  }
+  __syncthreads();
+  using Policy = exchange_policy<UK, UV>;
+  const Policy policy{coding, exch_shift<UK>((int)plan->field), s_lut, s_dst_k, s_dst_v};
+  const unsigned my_bin_base = threadIdx.x < MAX_BUCKETS ? (unsigned)plan->send_offset[threadIdx.x] : 0u;
+  sweep_tiles<UK, UV, HAS_V, Policy, LB, IPT>(src, vsrc, n, &hdr->ticket, policy, my_bin_base, lookback, &hdr->error, smem_raw);
+}
+
 // ---------------------------------------------------------------- 4. copy back after an odd number of passes
 template <class UK, class UV, bool HAS_V>
 __global__ void __launch_bounds__(256)
@@ -618,6 +778,7 @@ cudaError_t radix_sort_async(UK* keys_a, UK* keys_b, UV* vals_a, UV* vals_b, siz
   if ((e = cudaFuncSetAttribute(hk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hist_smem)) != cudaSuccess) return e;
   { timed_launch tl(KID_RADIX_HIST, stream);
   hk<<<(unsigned)hist_grid, HIST_BLOCK, hist_smem, stream>>>(keys_a, n, coding, first_pass, num_passes, ctrl); }
+  log_launch("radix_hist_kernel", hist_grid, HIST_BLOCK, hist_smem, n, stream);
   radix_scan_hist_kernel<><<<num_passes, RADIX_BINS, 0, stream>>>(ctrl, n, first_pass);
 
   const size_t smem = onesweep_smem_bytes<KB, VB>();
@@ -638,6 +799,7 @@ cudaError_t radix_sort_async(UK* keys_a, UK* keys_b, UV* vals_a, UV* vals_b, siz
     else
       k64<<<grid, ONESWEEP_BLOCK, smem, stream>>>(keys_a, keys_b, vals_a, vals_b, (unsigned)n, coding, first_pass + p, first_pass, ctrl,
                                                   reinterpret_cast<unsigned long long*>(lb), hdr);
+    log_launch("onesweep_kernel", grid, ONESWEEP_BLOCK, smem, n, stream);
   }
   size_t cb_grid = (n + 256 * 8 - 1) / (256 * 8);
   if (cb_grid > (size_t)di.sm_count * 8) cb_grid = (size_t)di.sm_count * 8;
@@ -682,6 +844,51 @@ cudaError_t bucket_scatter_async(const UK* keys, const UV* vals, size_t n, key_c
   const unsigned grid = (unsigned)(tiles_all < (size_t)di.sm_count * ONESWEEP_CTAS_PER_SM ? tiles_all : (size_t)di.sm_count * ONESWEEP_CTAS_PER_SM);
   kern<<<grid, ONESWEEP_BLOCK, smem, stream>>>(keys, vals, (unsigned)n, coding, d_splitters, buckets, table,
                                                reinterpret_cast<uint32_t*>(base + sizeof(ws_header)), reinterpret_cast<ws_header*>(base));
+  return cudaGetLastError();
+}
+
+// row[0, fields * 4096 + EXCH_ROW_TAIL) = this GPU's histograms, the tag and n; no sync
+template <class UK>
+cudaError_t exchange_hist_async(const UK* keys, size_t n, key_coding coding, unsigned long long tag, unsigned* d_row, cudaStream_t stream) {
+  constexpr int F = exch_fields<UK>();
+  cudaError_t e = cudaMemsetAsync(d_row, 0, exch_row_words(F) * sizeof(unsigned), stream);
+  if (e != cudaSuccess) return e;
+  const device_info& di = current_device_info();
+  size_t grid = (n + 1024 * 8 - 1) / (1024 * 8);
+  if (grid > (size_t)di.sm_count) grid = (size_t)di.sm_count;
+  if (grid < 1) grid = 1;
+  const size_t smem = (size_t)F * EXCH_BINS * sizeof(unsigned);
+  auto kern = exchange_hist_kernel<UK>;
+  if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
+  kern<<<(unsigned)grid, 1024, smem, stream>>>(keys, n, coding, tag, d_row);
+  return cudaGetLastError();
+}
+
+inline cudaError_t exchange_plan_async(const unsigned* d_rows, int ranks, int rank, int fields, exchange_plan* d_plan, cudaStream_t stream) {
+  if (ranks < 1 || ranks > MAX_BUCKETS || rank < 0 || rank >= ranks || fields < 1 || fields > EXCH_MAX_FIELDS) return cudaErrorInvalidValue;
+  exchange_plan_kernel<><<<1, 1024, 0, stream>>>(d_rows, ranks, rank, fields, d_plan);
+  return cudaGetLastError();
+}
+
+// Stable scatter by the plan's bins (see exchange_scatter_kernel); n < 2^30; workspace as bucket_scatter.  No sync.
+template <class UK, class UV, bool HAS_V>
+cudaError_t exchange_scatter_async(const UK* keys, const UV* vals, size_t n, key_coding coding, const exchange_plan* d_plan,
+                                   const bucket_table<UK, UV>& table, void* ws, cudaStream_t stream) {
+  constexpr int KB = sizeof(UK);
+  constexpr int VB = HAS_V ? sizeof(UV) : 0;
+  constexpr int IPT = onesweep_tuning<KB, VB>::IPT;
+  if (n >= (1ull << 30)) return cudaErrorInvalidValue;
+  cudaError_t e = cudaMemsetAsync(ws, 0, bucket_scatter_workspace_bytes<KB, VB>(n), stream);
+  if (e != cudaSuccess || n == 0) return e;
+  char* base = static_cast<char*>(ws);
+  auto kern = exchange_scatter_kernel<UK, UV, HAS_V, uint32_t, IPT>;
+  const size_t smem = onesweep_smem_bytes<KB, VB>();
+  if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
+  const device_info& di = current_device_info();
+  const size_t tiles_all = sweep_tiles_of<KB, VB>(n);
+  const unsigned grid = (unsigned)(tiles_all < (size_t)di.sm_count * ONESWEEP_CTAS_PER_SM ? tiles_all : (size_t)di.sm_count * ONESWEEP_CTAS_PER_SM);
+  kern<<<grid, ONESWEEP_BLOCK, smem, stream>>>(keys, vals, (unsigned)n, coding, d_plan, table, reinterpret_cast<uint32_t*>(base + sizeof(ws_header)),
+                                               reinterpret_cast<ws_header*>(base));
   return cudaGetLastError();
 }
 

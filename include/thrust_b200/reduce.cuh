@@ -94,7 +94,7 @@ reduce_kernel(InIt in, size_t n, AccT init, Op op, AccT* partials, unsigned* par
   __threadfence();
   opt<AccT> f; f.has = false;
   for (unsigned b = threadIdx.x; b < gridDim.x; b += REDUCE_BLOCK) {
-    if (__ldcg(partial_has + b)) f.append(__ldcg(partials + b), op);
+    if (__ldcg(partial_has + b)) f.append(load_cg_any(partials + b), op);
   }
   __syncthreads();
   f = block_reduce_opt(f, op, smem);
@@ -138,6 +138,7 @@ cudaError_t reduce_async(InIt in, size_t n, AccT init, Op op, AccT* d_out, void*
         int grid = reduce_grid(n / VEC);
         timed_launch tl(KID_REDUCE, stream);
         reduce_kernel<InIt, AccT, Op, VEC><<<grid, REDUCE_BLOCK, 0, stream>>>(in, n, init, op, partials, has, &hdr->ticket, d_out);
+        log_launch("reduce_kernel (16-byte loads)", grid, REDUCE_BLOCK, 0, n, stream);
         return cudaGetLastError();
       }
     }
@@ -145,6 +146,7 @@ cudaError_t reduce_async(InIt in, size_t n, AccT init, Op op, AccT* d_out, void*
   int grid = reduce_grid(n);
   timed_launch tl(KID_REDUCE, stream);
   reduce_kernel<InIt, AccT, Op, 0><<<grid, REDUCE_BLOCK, 0, stream>>>(in, n, init, op, partials, has, &hdr->ticket, d_out);
+  log_launch("reduce_kernel (generic iterator)", grid, REDUCE_BLOCK, 0, n, stream);
   return cudaGetLastError();
 }
 

@@ -81,7 +81,7 @@ reduce_by_key_kernel(KeyIt keys, ValIt vals, KeyOutIt keys_out, ValOutIt vals_ou
 #pragma unroll
     for (int i = 0; i < IPT; ++i) {
       const unsigned c = threadIdx.x + i * RBK_BLOCK;
-      if (c < tile_n) { s_key[c] = keys[tile_base + c]; s_val[c] = (V)vals[tile_base + c]; }
+      if (c < tile_n) { stash(&s_key[c], (K)keys[tile_base + c]); stash(&s_val[c], (V)vals[tile_base + c]); }
     }
   }
   if (threadIdx.x == 0 && tile_base > 0) s_prev = keys[tile_base - 1];
@@ -129,8 +129,8 @@ reduce_by_key_kernel(KeyIt keys, ValIt vals, KeyOutIt keys_out, ValOutIt vals_ou
       if ((unsigned)j < mine) {
         if ((heads >> j) & 1) {
           const unsigned r = (unsigned)(run - head_off);
-          s_key[r] = k[j];
-          s_val[r] = acc;                                           // total of the run that ends before this head (unused for run 0)
+          stash(&s_key[r], k[j]);
+          stash(&s_val[r], acc);                                           // total of the run that ends before this head (unused for run 0)
           ++run;
           acc = x[j];
         } else if (j > 0 || pre[0].has) {

@@ -609,6 +609,7 @@ cudaError_t scan_async(InIt in, OutIt out, size_t n, T init, bool has_init, Op o
               if (e3 != cudaSuccess) return e3;
               timed_launch tl(KID_SCAN, stream);
               kern<<<(unsigned)grid, SCAN_BLOCK, 0, stream>>>(in, out, n, tiles2, tpc, init, has_init, op, tsw, hdr);
+              log_launch("scan_window_kernel", grid, SCAN_BLOCK, 0, n, stream);
               return cudaGetLastError();
             }
           }
@@ -621,6 +622,7 @@ cudaError_t scan_async(InIt in, OutIt out, size_t n, T init, bool has_init, Op o
           timed_launch tl(KID_SCAN, stream);
           scan_chunk_reduce_kernel<T, Op, VEC, IPT2><<<(unsigned)chunks, SCAN_BLOCK, 0, stream>>>(in, n, tiles2, tiles_per_chunk, op, partials);
           scan_chunk_kernel<T, Op, INCLUSIVE, VEC, IPT2><<<(unsigned)chunks, SCAN_BLOCK, 0, stream>>>(in, out, n, tiles2, tiles_per_chunk, init, has_init, op, partials);
+          log_launch("scan_chunk_reduce_kernel + scan_chunk_kernel", chunks, SCAN_BLOCK, 0, n, stream);
           return cudaGetLastError();
         }
       }
@@ -630,6 +632,9 @@ cudaError_t scan_async(InIt in, OutIt out, size_t n, T init, bool has_init, Op o
   ts.bind(base + sizeof(ws_header), tiles + 1);
   cudaError_t e = cudaMemsetAsync(base, 0, scan_workspace_bytes<T>(n), stream);
   if (e != cudaSuccess) return e;
+#ifdef TB200_TEST_HOOKS
+  if (test_hook_flags() & 1u) { if ((e = cudaMemsetAsync(&hdr->flags, 1, 1, stream)) != cudaSuccess) return e; }
+#endif
   timed_launch tl(KID_SCAN, stream);
   if constexpr (ptrs) {
     using In = typename std::remove_cv<typename std::remove_pointer<InIt>::type>::type;
@@ -640,11 +645,13 @@ cudaError_t scan_async(InIt in, OutIt out, size_t n, T init, bool has_init, Op o
       if (vectors) {
         constexpr int VEC = 16 / sizeof(T);
         scan_kernel<InIt, OutIt, T, Op, INCLUSIVE, VEC, IPT><<<(unsigned)tiles, SCAN_BLOCK, 0, stream>>>(in, out, n, init, has_init, op, ts, hdr);
+        log_launch("scan_kernel (16-byte loads)", tiles, SCAN_BLOCK, 0, n, stream);
         return cudaGetLastError();
       }
     }
   }
   scan_kernel<InIt, OutIt, T, Op, INCLUSIVE, 1, IPT><<<(unsigned)tiles, SCAN_BLOCK, 0, stream>>>(in, out, n, init, has_init, op, ts, hdr);
+  log_launch("scan_kernel (generic iterator)", tiles, SCAN_BLOCK, 0, n, stream);
   return cudaGetLastError();
 }
 

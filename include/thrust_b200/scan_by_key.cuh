@@ -52,7 +52,7 @@ scan_by_key_kernel(KeyIt keys, ValIt vals, OutIt out, size_t n, V init, Eq key_e
 #pragma unroll
     for (int i = 0; i < IPT; ++i) {
       const unsigned c = threadIdx.x + i * RBK_BLOCK;
-      if (c < tile_n) { s_key[c] = keys[tile_base + c]; s_val[c] = (V)vals[tile_base + c]; }
+      if (c < tile_n) { stash(&s_key[c], (K)keys[tile_base + c]); stash(&s_val[c], (V)vals[tile_base + c]); }
     }
   }
   if (threadIdx.x == 0 && tile_base > 0) s_prev = keys[tile_base - 1];

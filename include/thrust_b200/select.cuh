@@ -131,8 +131,8 @@ select_kernel(InIt in, StIt stencil, SelIt out_sel, RejIt out_rej, size_t n, Pre
     const unsigned local0 = warp * WCHUNK + (v * 32 + lane) * VEC;
 #pragma unroll
     for (int k = 0; k < VEC; ++k) {
-      if ((keep[v] >> k) & 1) stage[sel_rank++] = x[v][k];
-      else if (KEEP_REJECTS && local0 + k < tile_n) stage[tile_nsel + (local0 + k - sel_rank)] = x[v][k];
+      if ((keep[v] >> k) & 1) stash(&stage[sel_rank++], x[v][k]);
+      else if (KEEP_REJECTS && local0 + k < tile_n) stash(&stage[tile_nsel + (local0 + k - sel_rank)], x[v][k]);
     }
   }
   __syncthreads();
@@ -154,9 +154,9 @@ select_kernel(InIt in, StIt stencil, SelIt out_sel, RejIt out_rej, size_t n, Pre
 
 // Second half of the in-place partition: scratch holds kept items at the front and dropped items
 // mirrored from the back; write them back to `data` with the dropped half un-mirrored.
-template <class T>
+template <class OutIt, class T>   // OutIt: a pointer or any random-access iterator (a zip_iterator, ...)
 __global__ void __launch_bounds__(256)
-partition_finish_kernel(T* data, const T* scratch, size_t n, const ws_header* hdr) {
+partition_finish_kernel(OutIt data, const T* scratch, size_t n, const ws_header* hdr) {
   const size_t nsel = (size_t)hdr->count;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) data[i] = i < nsel ? scratch[i] : scratch[n - 1 - (i - nsel)];
@@ -231,7 +231,7 @@ cudaError_t partition_finish_async(T* data, const T* scratch, size_t n, const vo
   const device_info& di = current_device_info();
   size_t grid = (n + 256 * 8 - 1) / (256 * 8);
   if (grid > (size_t)di.sm_count * 8) grid = (size_t)di.sm_count * 8;
-  partition_finish_kernel<T><<<(unsigned)grid, 256, 0, stream>>>(data, scratch, n, reinterpret_cast<const ws_header*>(ws));
+  partition_finish_kernel<<<(unsigned)grid, 256, 0, stream>>>(data, scratch, n, reinterpret_cast<const ws_header*>(ws));
   return cudaGetLastError();
 }
 

@@ -27,12 +27,17 @@
 #pragma once
 
 #include <thrust/detail/config.h>
+#include <thrust/detail/execute_with_allocator.h>
 #include <thrust/detail/raw_pointer_cast.h>
 #include <thrust/detail/temporary_array.h>
 #include <thrust/distance.h>
 #include <thrust/execution_policy.h>
 #include <thrust/functional.h>
 #include <thrust/iterator/iterator_traits.h>
+#include <thrust/iterator/transform_iterator.h>
+#include <thrust/iterator/zip_iterator.h>
+#include <thrust/zip_function.h>
+#include <thrust/detail/internal_functional.h>
 #include <thrust/pair.h>
 #include <thrust/system/cuda/detail/par.h>
 #include <thrust/system/cuda/detail/util.h>
@@ -62,6 +67,14 @@ template <> struct is_overlaid_policy<par_nosync_t> : std::true_type {};
 template <> struct is_overlaid_policy<execute_on_stream> : std::true_type {};
 template <> struct is_overlaid_policy<execute_on_stream_nosync> : std::true_type {};
 template <> struct is_overlaid_policy<tag> : std::true_type {};
+// thrust::cuda::par(alloc), par.on(stream)(alloc), par_nosync(alloc): the same kernels, with
+// temporary storage drawn from the caller's allocator (thrust/system/cuda/detail/par.h:86-108,
+// thrust/detail/allocator_aware_execution_policy.h)
+template <template <class> class Base> struct is_cuda_policy_base : std::false_type {};
+template <> struct is_cuda_policy_base<execute_on_stream_base> : std::true_type {};
+template <> struct is_cuda_policy_base<execute_on_stream_nosync_base> : std::true_type {};
+template <class Alloc, template <class> class Base>
+struct is_overlaid_policy<thrust::detail::execute_with_allocator<Alloc, Base>> : is_cuda_policy_base<Base> {};
 template <class P> using enable_for = typename std::enable_if<is_overlaid_policy<P>::value, int>::type;
 
 template <class It> using value_t = typename thrust::iterator_traits<It>::value_type;
@@ -72,11 +85,17 @@ auto unwrap(It it) -> decltype(thrust::raw_pointer_cast(&*it)) { return thrust::
 template <class It, typename std::enable_if<!thrust::is_contiguous_iterator<It>::value, int>::type = 0>
 It unwrap(It it) { return it; }
 
-// Thrust functors -> this library's (so that the arithmetic fast paths are recognised); user functors pass through
-template <class F> struct map_op { using type = F; static type get(const F& f) { return f; } };
-template <class T> struct map_op<thrust::plus<T>> { using type = ::tb200::plus_op; static type get(const thrust::plus<T>&) { return {}; } };
-template <class T> struct map_op<thrust::minimum<T>> { using type = ::tb200::min_op; static type get(const thrust::minimum<T>&) { return {}; } };
-template <class T> struct map_op<thrust::maximum<T>> { using type = ::tb200::max_op; static type get(const thrust::maximum<T>&) { return {}; } };
+// Thrust functors -> this library's (so that the arithmetic fast paths are recognised), but only
+// where they mean the same: thrust::plus<Acc> or the transparent thrust::plus<> on an accumulator of
+// type Acc.  thrust::plus<int> on floats truncates its operands (testing/scan.cu:258-264 relies on
+// it), so it stays the caller's functor, like every user functor.
+template <class F, class Acc> struct map_op { using type = F; static type get(const F& f) { return f; } };
+template <class Acc> struct map_op<thrust::plus<Acc>, Acc> { using type = ::tb200::plus_op; static type get(const thrust::plus<Acc>&) { return {}; } };
+template <class Acc> struct map_op<thrust::plus<void>, Acc> { using type = ::tb200::plus_op; static type get(const thrust::plus<void>&) { return {}; } };
+template <class Acc> struct map_op<thrust::minimum<Acc>, Acc> { using type = ::tb200::min_op; static type get(const thrust::minimum<Acc>&) { return {}; } };
+template <class Acc> struct map_op<thrust::minimum<void>, Acc> { using type = ::tb200::min_op; static type get(const thrust::minimum<void>&) { return {}; } };
+template <class Acc> struct map_op<thrust::maximum<Acc>, Acc> { using type = ::tb200::max_op; static type get(const thrust::maximum<Acc>&) { return {}; } };
+template <class Acc> struct map_op<thrust::maximum<void>, Acc> { using type = ::tb200::max_op; static type get(const thrust::maximum<void>&) { return {}; } };
 
 template <class Comp, class K> struct radix_order { static constexpr int value = -1; };                       // -1: not a radix order
 template <class K> struct radix_order<thrust::less<K>, K> { static constexpr int value = 0; };
@@ -129,7 +148,7 @@ T reduce_n(Policy& policy, InputIt first, Size num_items, T init, BinaryOp binar
   if (num_items <= 0) return init;                                                    // reduce.h:863-864
   ov::scratch<Policy> tmp(policy, ::tb200::reduce_workspace_bytes<T>() + 256);
   T* d_out = reinterpret_cast<T*>(tmp.at(ov::up256(::tb200::reduce_workspace_bytes<T>())));
-  cudaError_t e = ::tb200::reduce_async(ov::unwrap(first), (std::size_t)num_items, init, ov::map_op<BinaryOp>::get(binary_op), d_out, tmp.at(),
+  cudaError_t e = ::tb200::reduce_async(ov::unwrap(first), (std::size_t)num_items, init, ov::map_op<BinaryOp, T>::get(binary_op), d_out, tmp.at(),
                                         cuda_cub::stream(policy));
   cuda_cub::throw_on_error(e, "reduce: launch failed");
   T result;
@@ -158,7 +177,7 @@ template <bool INCLUSIVE, class Policy, class InputIt, class OutputIt, class T, 
 OutputIt scan_n(Policy& policy, InputIt first, std::size_t n, OutputIt result, T init, bool has_init, ScanOp op) {
   if (n == 0) return result;
   scratch<Policy> tmp(policy, ::tb200::scan_workspace_bytes<T>(n));
-  cudaError_t e = ::tb200::scan_async<INCLUSIVE>(unwrap(first), unwrap(result), n, init, has_init, map_op<ScanOp>::get(op), tmp.at(), cuda_cub::stream(policy));
+  cudaError_t e = ::tb200::scan_async<INCLUSIVE>(unwrap(first), unwrap(result), n, init, has_init, map_op<ScanOp, T>::get(op), tmp.at(), cuda_cub::stream(policy));
   finish(policy, e, tmp.at(), INCLUSIVE ? "inclusive_scan failed" : "exclusive_scan failed");
   return result + n;
 }
@@ -427,7 +446,7 @@ thrust::pair<KeyOutIt, ValOutIt> reduce_by_key(Policy& policy, KeyIt keys_first,
   if (n == 0) return thrust::make_pair(keys_output, values_output);
   ov::scratch<Policy> tmp(policy, ::tb200::rbk_workspace_bytes<K, V>(n));
   cudaError_t e = ::tb200::reduce_by_key_async(ov::unwrap(keys_first), ov::unwrap(values_first), ov::unwrap(keys_output), ov::unwrap(values_output), n, K(), V(),
-                                              binary_pred, ov::map_op<BinaryOp>::get(binary_op), nullptr, tmp.at(), cuda_cub::stream(policy));
+                                              binary_pred, ov::map_op<BinaryOp, V>::get(binary_op), nullptr, tmp.at(), cuda_cub::stream(policy));
   const std::size_t runs = ov::finish(policy, e, tmp.at(), "reduce_by_key failed");
   return thrust::make_pair(keys_output + runs, values_output + runs);
 }
@@ -453,7 +472,7 @@ OutIt inclusive_scan_by_key(Policy& policy, KeyIt key_first, KeyIt key_last, Val
   if (n == 0) return value_result;
   ov::scratch<Policy> tmp(policy, ::tb200::scan_by_key_workspace_bytes<K, V>(n));
   cudaError_t e = ::tb200::scan_by_key_async<true>(ov::unwrap(key_first), ov::unwrap(value_first), ov::unwrap(value_result), n, K(), V(), binary_pred,
-                                                 ov::map_op<ScanOp>::get(scan_op), tmp.at(), cuda_cub::stream(policy));
+                                                 ov::map_op<ScanOp, V>::get(scan_op), tmp.at(), cuda_cub::stream(policy));
   ov::finish(policy, e, tmp.at(), "inclusive_scan_by_key failed");
   return value_result + n;
 }
@@ -474,7 +493,7 @@ OutIt exclusive_scan_by_key(Policy& policy, KeyIt key_first, KeyIt key_last, Val
   if (n == 0) return value_result;
   ov::scratch<Policy> tmp(policy, ::tb200::scan_by_key_workspace_bytes<K, V>(n));
   cudaError_t e = ::tb200::scan_by_key_async<false>(ov::unwrap(key_first), ov::unwrap(value_first), ov::unwrap(value_result), n, K(), init, binary_pred,
-                                                  ov::map_op<ScanOp>::get(scan_op), tmp.at(), cuda_cub::stream(policy));
+                                                  ov::map_op<ScanOp, V>::get(scan_op), tmp.at(), cuda_cub::stream(policy));
   ov::finish(policy, e, tmp.at(), "exclusive_scan_by_key failed");
   return value_result + n;
 }
@@ -599,3 +618,85 @@ thrust::pair<ItemsIt, ItemsIt> minmax_element(Policy& policy, ItemsIt first, Ite
 
 }  // namespace cuda_cub
 THRUST_NAMESPACE_END
+
+// ------------------------------------------------------------------------------------- callers of the above
+// count / count_if, inner_product, transform_reduce, transform_inclusive_scan / transform_exclusive_scan
+// and remove / remove_if / remove_copy(_if) are thin forwarders in the reference's backend
+// (thrust/system/cuda/detail/{count.h:56, inner_product.h:64, transform_reduce.h:59, transform_scan.h,
+// remove.h:38-134}); the stock ones hand their `execution_policy<Derived>&` on, which would reach the
+// stock reduce_n / scan / copy_if, so they are restated here on the concrete policy types.
+THRUST_NAMESPACE_BEGIN
+namespace cuda_cub {
+
+template <class Policy, class InputIt, class UnaryPred, tb200_overlay::enable_for<Policy> = 0>
+typename thrust::iterator_traits<InputIt>::difference_type count_if(Policy& policy, InputIt first, InputIt last, UnaryPred unary_pred) {
+  using size_type = typename thrust::iterator_traits<InputIt>::difference_type;
+  using flags_t = thrust::transform_iterator<UnaryPred, InputIt, size_type, size_type>;
+  return cuda_cub::reduce_n(policy, flags_t(first, unary_pred), thrust::distance(first, last), size_type(0), thrust::plus<size_type>());
+}
+template <class Policy, class InputIt, class Value, tb200_overlay::enable_for<Policy> = 0>
+typename thrust::iterator_traits<InputIt>::difference_type count(Policy& policy, InputIt first, InputIt last, const Value& value) {
+  return cuda_cub::count_if(policy, first, last, thrust::detail::equal_to_value<Value>(value));
+}
+
+template <class Policy, class InputIt1, class InputIt2, class T, class ReduceOp, class ProductOp, tb200_overlay::enable_for<Policy> = 0>
+T inner_product(Policy& policy, InputIt1 first1, InputIt1 last1, InputIt2 first2, T init, ReduceOp reduce_op, ProductOp product_op) {
+  const auto products = thrust::make_transform_iterator(thrust::make_zip_iterator(first1, first2), thrust::make_zip_function(product_op));
+  return cuda_cub::reduce_n(policy, products, thrust::distance(first1, last1), init, reduce_op);
+}
+template <class Policy, class InputIt1, class InputIt2, class T, tb200_overlay::enable_for<Policy> = 0>
+T inner_product(Policy& policy, InputIt1 first1, InputIt1 last1, InputIt2 first2, T init) {
+  return cuda_cub::inner_product(policy, first1, last1, first2, init, thrust::plus<T>(), thrust::multiplies<T>());
+}
+
+template <class Policy, class InputIt, class TransformOp, class T, class ReduceOp, tb200_overlay::enable_for<Policy> = 0>
+T transform_reduce(Policy& policy, InputIt first, InputIt last, TransformOp transform_op, T init, ReduceOp reduce_op) {
+  using transformed_t = thrust::transform_iterator<TransformOp, InputIt, T, T>;       // accumulates in the type of init
+  return cuda_cub::reduce_n(policy, transformed_t(first, transform_op), thrust::distance(first, last), init, reduce_op);
+}
+
+template <class Policy, class InputIt, class OutputIt, class TransformOp, class ScanOp, tb200_overlay::enable_for<Policy> = 0>
+OutputIt transform_inclusive_scan(Policy& policy, InputIt first, InputIt last, OutputIt result, TransformOp transform_op, ScanOp scan_op) {
+  using value_type = ::cuda::std::remove_cvref_t<thrust::detail::invoke_result_t<TransformOp, typename thrust::iterator_value<InputIt>::type>>;
+  using transformed_t = thrust::transform_iterator<TransformOp, InputIt, value_type, value_type>;   // the transformed value type (P0571)
+  return cuda_cub::inclusive_scan_n(policy, transformed_t(first, transform_op), thrust::distance(first, last), result, scan_op);
+}
+template <class Policy, class InputIt, class OutputIt, class TransformOp, class InitialValueType, class ScanOp, tb200_overlay::enable_for<Policy> = 0>
+OutputIt transform_exclusive_scan(Policy& policy, InputIt first, InputIt last, OutputIt result, TransformOp transform_op, InitialValueType init, ScanOp scan_op) {
+  using result_type = ::cuda::std::remove_cvref_t<InitialValueType>;                  // the initial value's type (P0571)
+  using transformed_t = thrust::transform_iterator<TransformOp, InputIt, result_type, result_type>;
+  return cuda_cub::exclusive_scan_n(policy, transformed_t(first, transform_op), thrust::distance(first, last), result, init, scan_op);
+}
+
+template <class Policy, class InputIt, class Predicate, tb200_overlay::enable_for<Policy> = 0>
+InputIt remove_if(Policy& policy, InputIt first, InputIt last, Predicate predicate) {
+  return cuda_cub::copy_if(policy, first, last, first, thrust::not_fn(predicate));    // in place: stable compaction onto itself
+}
+template <class Policy, class InputIt, class StencilIt, class Predicate, tb200_overlay::enable_for<Policy> = 0>
+InputIt remove_if(Policy& policy, InputIt first, InputIt last, StencilIt stencil, Predicate predicate) {
+  return cuda_cub::copy_if(policy, first, last, stencil, first, thrust::not_fn(predicate));
+}
+template <class Policy, class InputIt, class T, tb200_overlay::enable_for<Policy> = 0>
+InputIt remove(Policy& policy, InputIt first, InputIt last, const T& value) {
+  return cuda_cub::remove_if(policy, first, last, thrust::detail::equal_to_value<T>(value));
+}
+template <class Policy, class InputIt, class OutputIt, class Predicate, tb200_overlay::enable_for<Policy> = 0>
+OutputIt remove_copy_if(Policy& policy, InputIt first, InputIt last, OutputIt result, Predicate predicate) {
+  return cuda_cub::copy_if(policy, first, last, result, thrust::not_fn(predicate));
+}
+template <class Policy, class InputIt, class StencilIt, class OutputIt, class Predicate, tb200_overlay::enable_for<Policy> = 0>
+OutputIt remove_copy_if(Policy& policy, InputIt first, InputIt last, StencilIt stencil, OutputIt result, Predicate predicate) {
+  return cuda_cub::copy_if(policy, first, last, stencil, result, thrust::not_fn(predicate));
+}
+template <class Policy, class InputIt, class OutputIt, class T, tb200_overlay::enable_for<Policy> = 0>
+OutputIt remove_copy(Policy& policy, InputIt first, InputIt last, OutputIt result, const T& value) {
+  return cuda_cub::remove_copy_if(policy, first, last, result, thrust::detail::equal_to_value<T>(value));
+}
+
+}  // namespace cuda_cub
+THRUST_NAMESPACE_END
+
+// thrust::async::{reduce, inclusive_scan, exclusive_scan, sort}: needs the installation's asynchronous algorithms (C++14)
+#if !defined(THRUST_B200_NO_ASYNC_OVERLAY) && __has_include(<thrust/system/cuda/detail/async/customization.h>)
+#include "thrust_async_overlay.cuh"
+#endif

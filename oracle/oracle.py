@@ -25,10 +25,13 @@ PREDS = {"mod_eq": 0, "lt": 1, "ge": 2, "ne": 3}
 
 
 def build(which=("port", "ref"), thrust_ref=None):
-    """Compile the oracle libraries with oracle/Makefile.  `ref` needs the reference checkout
-    (THRUST_REF, default /root/reference); it is skipped silently when that is absent."""
+    """Compile the oracle libraries with oracle/Makefile.  `ref` needs a checkout of the reference
+    (Thrust 1.14.0): the directory named by THRUST_REF, else baseline/_ref in this repository, else a
+    directory `reference` beside the repository; it is skipped silently when none has the headers."""
     env = dict(os.environ)
-    ref_dir = thrust_ref or env.get("THRUST_REF", "/root/reference")
+    repo = os.path.dirname(_HERE)
+    candidates = [thrust_ref, env.get("THRUST_REF"), os.path.join(repo, "baseline", "_ref"), os.path.join(os.path.dirname(repo), "reference")]
+    ref_dir = next((c for c in candidates if c and os.path.isfile(os.path.join(c, "thrust", "version.h"))), "")
     if "port" in which:
         subprocess.check_call(["make", "-C", _HERE, "port"], env=env)
     if "ref" in which and os.path.isfile(os.path.join(ref_dir, "thrust", "version.h")):

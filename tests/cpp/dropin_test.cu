@@ -5,6 +5,9 @@
 //
 //   nvcc -std=c++17 -gencode arch=compute_100a,code=sm_100a --extended-lambda -I<repo>/include \
 //        -include thrust_b200/thrust_overlay.cuh tests/cpp/dropin_test.cu -o dropin_test
+#include <thrust/async/reduce.h>
+#include <thrust/async/scan.h>
+#include <thrust/async/sort.h>
 #include <thrust/copy.h>
 #include <thrust/device_vector.h>
 #include <thrust/execution_policy.h>
@@ -41,6 +44,19 @@ static unsigned long long mix(unsigned long long i) {
 }
 struct is_even { __host__ __device__ bool operator()(int x) const { return (x & 1) == 0; } };
 struct square { __host__ __device__ long long operator()(int x) const { return (long long)x * x; } };
+// a struct accumulator (examples/minmax.cu in the reference) and a 32-byte key with its own comparator
+struct lohi { int lo, hi; };
+struct to_lohi { __host__ __device__ lohi operator()(int x) const { lohi r; r.lo = x; r.hi = x; return r; } };
+struct lohi_merge { __host__ __device__ lohi operator()(const lohi& a, const lohi& b) const { lohi r; r.lo = a.lo < b.lo ? a.lo : b.lo; r.hi = a.hi > b.hi ? a.hi : b.hi; return r; } };
+struct wide { unsigned long long k; unsigned long long pad[3]; };
+struct wide_less { __host__ __device__ bool operator()(const wide& a, const wide& b) const { return a.k < b.k; } };
+// an allocator of the caller's own, as handed to thrust::cuda::par(alloc): counts what it serves
+struct counting_allocator {
+  typedef char value_type;
+  int* served;
+  char* allocate(std::ptrdiff_t bytes) { ++*served; char* p = nullptr; if (cudaMalloc(&p, (size_t)bytes) != cudaSuccess) throw std::bad_alloc(); return p; }
+  void deallocate(char* p, size_t) { cudaFree(p); }
+};
 struct by_first { template <class A, class B> __host__ __device__ bool operator()(const A& a, const B& b) const { return thrust::get<0>(a) < thrust::get<0>(b); } };
 
 int main() {
@@ -161,9 +177,57 @@ int main() {
     thrust::merge(da.begin(), da.end(), db.begin(), db.end(), dmo.begin());
     gm = dmo; CHECK(std::equal(hm.begin(), hm.end(), gm.begin())); }
 
+  // a struct accumulator through transform_reduce / reduce
+  { lohi init; init.lo = h[0]; init.hi = h[0];
+    lohi r = thrust::reduce(thrust::device, thrust::make_transform_iterator(d.begin(), to_lohi()), thrust::make_transform_iterator(d.end(), to_lohi()), init, lohi_merge());
+    CHECK(r.lo == *std::min_element(h.begin(), h.end()) && r.hi == *std::max_element(h.begin(), h.end())); }
+
+  // 32-byte keys with a user comparator: comparison sort, sort_by_key and merge size their tiles by sizeof
+  { const int nw = 100003; std::vector<wide> hw(nw); for (int i = 0; i < nw; ++i) { hw[i].k = mix(i) >> 44; hw[i].pad[0] = i; hw[i].pad[1] = hw[i].pad[2] = 0; }
+    thrust::device_vector<wide> dw(hw.begin(), hw.end());
+    thrust::stable_sort(thrust::device, dw.begin(), dw.end(), wide_less());
+    std::stable_sort(hw.begin(), hw.end(), [](const wide& a, const wide& b) { return a.k < b.k; });
+    thrust::host_vector<wide> gw = dw; ok = true; for (int i = 0; i < nw && ok; ++i) ok = gw[i].k == hw[i].k && gw[i].pad[0] == hw[i].pad[0];
+    CHECK(ok);
+    thrust::device_vector<wide> dk2(hw.rbegin(), hw.rend()); thrust::device_vector<int> dv2(nw); thrust::sequence(dv2.begin(), dv2.end());
+    thrust::stable_sort_by_key(thrust::device, dk2.begin(), dk2.end(), dv2.begin(), wide_less());
+    gw = dk2; ok = true; for (int i = 1; i < nw && ok; ++i) ok = gw[i - 1].k <= gw[i].k;
+    CHECK(ok);
+    thrust::device_vector<wide> dm2(2 * nw);
+    thrust::merge(thrust::device, dw.begin(), dw.end(), dk2.begin(), dk2.end(), dm2.begin(), wide_less());
+    gw = dm2; ok = true; for (int i = 1; i < 2 * nw && ok; ++i) ok = gw[i - 1].k <= gw[i].k;
+    CHECK(ok && gw.size() == (size_t)(2 * nw)); }
+
+  // thrust::cuda::par(alloc): the same kernels, temporary storage from the caller's allocator
+  { int served = 0; counting_allocator alloc; alloc.served = &served;
+    const unsigned long long before = thrust::cuda_cub::tb200_overlay::call_count();
+    CHECK(thrust::reduce(thrust::cuda::par(alloc), d.begin(), d.end(), 0LL, thrust::plus<long long>()) == want);
+    thrust::device_vector<int> ds(d.begin(), d.end());
+    thrust::sort(thrust::cuda::par(alloc).on(s), ds.begin(), ds.end());
+    std::vector<int> hsorted(h.begin(), h.end()); std::sort(hsorted.begin(), hsorted.end());
+    got = ds; CHECK(std::equal(hsorted.begin(), hsorted.end(), got.begin()));
+    CHECK(served >= 2 && thrust::cuda_cub::tb200_overlay::call_count() == before + 2); }
+
+  // thrust::async: the same kernels without the final wait
+  { const unsigned long long before = thrust::cuda_cub::tb200_overlay::call_count();
+    auto fut = thrust::async::reduce(thrust::device, d.begin(), d.end(), 0LL, thrust::plus<long long>());
+    thrust::device_vector<int> din(small.begin(), small.end()), dout(n), dex(n);
+    auto e1 = thrust::async::inclusive_scan(thrust::device, din.begin(), din.end(), dout.begin());
+    auto e2 = thrust::async::exclusive_scan(thrust::device, din.begin(), din.end(), dex.begin(), 7);
+    thrust::device_vector<int> da2(d.begin(), d.end());
+    auto e3 = thrust::async::sort(thrust::device, da2.begin(), da2.end());
+    CHECK(fut.get() == want);
+    e1.wait(); e2.wait(); e3.wait();
+    std::vector<int> hi(n); std::partial_sum(small.begin(), small.end(), hi.begin());
+    got = dout; CHECK(std::equal(hi.begin(), hi.end(), got.begin()));
+    got = dex; ok = got[0] == 7; for (int i = 1; i < n && ok; ++i) ok = got[i] == hi[i - 1] + 7; CHECK(ok);
+    std::vector<int> hsorted(h.begin(), h.end()); std::sort(hsorted.begin(), hsorted.end());
+    got = da2; CHECK(std::equal(hsorted.begin(), hsorted.end(), got.begin()));
+    CHECK(thrust::cuda_cub::tb200_overlay::call_count() == before + 4); }
+
   // the overlay, not the stock CUB path, served these calls
   std::printf("overlay served %llu calls\n", thrust::cuda_cub::tb200_overlay::call_count());
-  CHECK(thrust::cuda_cub::tb200_overlay::call_count() == 28);
+  CHECK(thrust::cuda_cub::tb200_overlay::call_count() == 38);
   cudaStreamDestroy(s);
   if (cudaDeviceSynchronize() != cudaSuccess) { std::printf("FAILED: sticky CUDA error\n"); ++failures; }
   std::printf(failures ? "dropin_test: %d FAILURES\n" : "dropin_test: all checks passed\n", failures);

@@ -31,14 +31,24 @@ def _worker(rank, world, port, out_dir):
         s = dg.scan_input_i32(n_total)
         assert np.array_equal(sharded.sharded_scan(dev(s[lo:hi])).cpu().numpy(), o.inclusive_scan(s)[lo:hi])
         assert np.array_equal(sharded.sharded_scan(dev(s[lo:hi]), exclusive=True, init=9).cpu().numpy(), o.exclusive_scan(s, 9)[lo:hi])
+        # unsigned min/max with the top bit set and an empty shard (the all-reduce of the collective library would compare them as signed)
+        u = (dg.sort_keys_u32(n_total) | np.uint32(0x80000000)).astype(np.uint32)
+        part = u[lo:hi] if rank != world - 1 else u[:0]
+        ref_part = np.concatenate([u[r * n_total // world:(r + 1) * n_total // world] for r in range(world - 1)])
+        assert sharded.sharded_reduce(dev(part), np.uint32(0xFFFFFFFF), "min") == ref_part.min()
+        assert sharded.sharded_reduce(dev(part), np.uint32(0), "max") == ref_part.max()
+        skew = dg.sort_keys_u32(n_total).copy()
+        skew[: (7 * n_total) // 8] = 123456789           # 7/8 of the keys equal: one rank's receive buffer would overflow, sampled splitters take over
         for case, keys in (("uniform", dg.sort_keys_u32(n_total)), ("ties", (dg.sort_keys_u32(n_total) >> np.uint32(22)).astype(np.uint32)),
-                           ("u64", dg.sort_keys_u64_40bit(n_total))):
+                           ("u64", dg.sort_keys_u64_40bit(n_total)), ("skew", skew),
+                           ("f32", dg.sort_keys_u32(n_total).view(np.int32).astype(np.float32))):
             vals = np.arange(n_total, dtype=np.uint32)
-            # "scatter": one kernel per GPU stores every pair into its owner's receive buffer, then a local sort;
+            # "histogram": splitters from a digit histogram, one kernel per GPU stores every pair into its owner's receive buffer, local sort;
+            # "scatter": the same with sampled splitters;
             # "peer": merges read the pieces straight out of the other GPUs' memory (CUDA IPC + NVLink);
-            # "collective": NCCL all-to-all first.  Both must give the single-GPU result.
-            for mode in ("scatter", "peer", "collective"):
-                for repeat in range(2):                      # the second call reuses cached IPC mappings
+            # "collective": NCCL all-to-all first.  All must give the single-GPU result.
+            for mode in ("histogram", "scatter", "peer", "collective"):
+                for repeat in range(3):                      # later calls alternate receive buffers and reuse cached IPC mappings
                     k, v = sharded.sharded_sort_by_key(dev(keys[lo:hi]), dev(vals[lo:hi]), exchange=mode)
                 np.save(os.path.join(out_dir, f"{case}_k{rank}.npy"), k.cpu().numpy())
                 np.save(os.path.join(out_dir, f"{case}_v{rank}.npy"), v.cpu().numpy())

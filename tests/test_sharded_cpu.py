@@ -73,6 +73,15 @@ def _worker(rank, world, port, case, out_dir):
             want = np.int64(5) + dg.reduce_input(n_total).sum(dtype=np.int64)
             assert got == want, (got, want)
             assert sharded.sharded_reduce(x, np.int64(0), "max", ops=ops) == dg.reduce_input(n_total).max()
+            # unsigned accumulators with the top bit set, one empty shard: a signed all-reduce would get these wrong
+            for dt, top in ((np.uint32, np.uint32(1 << 31)), (np.uint64, np.uint64(1 << 63))):
+                full = (dg.rand64(9, n_total).astype(dt) | top).astype(dt)
+                mine = full[lo:hi] if rank != world - 1 else full[:0]
+                seen = full[:(world - 1) * n_total // world]
+                assert sharded.sharded_reduce(torch.from_numpy(mine.copy()), np.asarray(np.iinfo(dt).max, dt)[()], "min", ops=ops) == seen.min()
+                assert sharded.sharded_reduce(torch.from_numpy(mine.copy()), np.asarray(0, dt)[()], "max", ops=ops) == seen.max()
+            f = np.full(4, -np.inf, np.float32)
+            assert sharded.sharded_reduce(torch.from_numpy(f), np.float32(-np.inf), "max", ops=ops) == -np.inf
         elif case == "scan":
             full = dg.scan_input_i32(n_total)
             x = torch.from_numpy(full[lo:hi].copy())

@@ -68,5 +68,38 @@ def build(force=False, verbose=False):
     return LIB
 
 
+SHORTWAIT_LIB = os.path.join(HERE, "libthrust_b200_shortwait.so")
+SHORTWAIT_SOURCES = ["abi_scan.cu", "abi_reduce.cu", "abi_util.cu"]
+SHORTWAIT_FLAGS = ["-DTB200_SPIN_LIMIT=64", "-DTB200_TEST_HOOKS"]
+
+
+def build_shortwait(force=False):
+    """A TEST build of the scan entry points: the bound on every inter-CTA wait is 64 polls instead
+    of 2^23, and tb200_test_hooks(1) makes the first tile of a single-pass scan withhold its
+    descriptor.  tests/test_gpu_failure_path.py uses it to show that a wait that runs out makes the
+    kernel RETURN with the status word set, which the host turns into an exception.  Nothing else
+    loads this library."""
+    obj_dir = os.path.join(OBJ_DIR, "shortwait")
+    os.makedirs(obj_dir, exist_ok=True)
+    hdr_time = _newest_header()
+    objs, stale = [], False
+    for name in SHORTWAIT_SOURCES:
+        src = os.path.join(CSRC, name)
+        obj = os.path.join(obj_dir, name[:-3] + ".o")
+        objs.append(obj)
+        if force or not os.path.isfile(obj) or os.path.getmtime(obj) < max(os.path.getmtime(src), hdr_time):
+            cmd = [_nvcc()] + NVCC_FLAGS + SHORTWAIT_FLAGS + ["-c", src, "-o", obj]
+            r = subprocess.run(cmd, capture_output=True, text=True)
+            if r.returncode != 0:
+                raise RuntimeError("nvcc failed for %s:\n%s\n%s" % (src, r.stdout, r.stderr))
+            stale = True
+    if stale or not os.path.isfile(SHORTWAIT_LIB):
+        r = subprocess.run([_nvcc(), "-shared", "-o", SHORTWAIT_LIB] + objs + ["-lcudart"], capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("link failed:\n%s\n%s" % (r.stdout, r.stderr))
+    return SHORTWAIT_LIB
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose=True))
+    print(build_shortwait(force="--force" in sys.argv))

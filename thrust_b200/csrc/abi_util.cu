@@ -55,3 +55,8 @@ TB200_API int tb200_lower_bound(const void* d_sorted, size_t n, const void* d_ne
     return (int)cudaGetLastError();
   });
 }
+
+#ifdef TB200_TEST_HOOKS
+// Exported by the test build only (thrust_b200.build.build_shortwait): see test_hook_flags().
+TB200_API int tb200_test_hooks(unsigned flags) { tb200::test_hook_flags() = flags; return 0; }
+#endif

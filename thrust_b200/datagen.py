@@ -21,6 +21,15 @@ def rand64(seed, n, start=0):
         return z ^ (z >> np.uint64(31))
 
 
+def rand64_at(seed, idx):
+    """The 64-bit values of stream `seed` at the counters in `idx` (any integer array)."""
+    with np.errstate(over="ignore"):
+        z = np.asarray(idx).astype(np.uint64) + np.uint64(((seed + 1) * _GOLDEN) & 0xFFFFFFFFFFFFFFFF)
+        z = (z ^ (z >> np.uint64(30))) * _M1
+        z = (z ^ (z >> np.uint64(27))) * _M2
+        return z ^ (z >> np.uint64(31))
+
+
 def reduce_input(n, seed=0, start=0):
     """config 1: int32 uniform in [-2^20, 2^20)."""
     return ((rand64(seed, n, start) >> np.uint64(43)).astype(np.int64) - (1 << 20)).astype(np.int32)
@@ -39,6 +48,11 @@ def scan_input_f32(n, seed=1, start=0):
 def sort_keys_u32(n, seed=2, start=0):
     """config 3a: uniform random 32-bit keys (values are the original index)."""
     return (rand64(seed, n, start) >> np.uint64(32)).astype(np.uint32)
+
+
+def sort_keys_u32_at(idx, seed=2):
+    """config 3a: the keys at the given original indices."""
+    return (rand64_at(seed, idx) >> np.uint64(32)).astype(np.uint32)
 
 
 def sort_keys_u64_40bit(n, seed=2, start=0):

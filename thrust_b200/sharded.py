@@ -27,8 +27,8 @@ from . import api
 
 _NP_IDENTITY = {
     "plus": lambda dt: np.zeros((), dt),
-    "min": lambda dt: np.array(np.finfo(dt).max if np.issubdtype(dt, np.floating) else np.iinfo(dt).max, dt),
-    "max": lambda dt: np.array(np.finfo(dt).min if np.issubdtype(dt, np.floating) else np.iinfo(dt).min, dt),
+    "min": lambda dt: np.array(np.inf if np.issubdtype(dt, np.floating) else np.iinfo(dt).max, dt),
+    "max": lambda dt: np.array(-np.inf if np.issubdtype(dt, np.floating) else np.iinfo(dt).min, dt),
 }
 _NP_OP = {"plus": np.add, "min": np.minimum, "max": np.maximum}
 _REDUCE_OP = {"plus": dist.ReduceOp.SUM, "min": dist.ReduceOp.MIN, "max": dist.ReduceOp.MAX}
@@ -113,6 +113,61 @@ class DeviceOps:
         api._call_with_ws("scatter", "tb200_bucket_scatter", api._ptr(keys), api._ptr(vals), keys.numel(), api.DTYPE_CODE[keys.dtype],
                           0 if vals is None else vals.element_size(), int(descending), api._ptr(splitters), m, kp, vp, off)
 
+    supports_histogram_exchange = True
+    _exchange_state = {}
+
+    def exchange_state(self, device, key_dtype, val_dtype):
+        """Per (device, types) state of the histogram exchange that outlives a call: two sets of receive
+        buffers used alternately (a result stays valid until the call after next, and a sender never
+        writes into a buffer its owner may still be sorting), their IPC handles, the peers' opened
+        pointers, and the small device arrays of the plan."""
+        key = (str(device), key_dtype, val_dtype)
+        st = self._exchange_state.get(key)
+        if st is None:
+            import ctypes as C
+            lib = api._lib.load()
+            words, plan_bytes, head = C.c_size_t(0), C.c_size_t(0), C.c_size_t(0)
+            api._check(lib.tb200_exchange_sizes(api.DTYPE_CODE[key_dtype], C.byref(words), C.byref(plan_bytes), C.byref(head)), "tb200_exchange_sizes")
+            st = {"sets": [None, None], "generation": [0, 0], "turn": 0, "known_tags": [None, None], "peer_ptrs": [None, None],
+                  "row_words": int(words.value), "plan_bytes": int(plan_bytes.value), "head_bytes": int(head.value),
+                  "row": torch.empty(int(words.value), dtype=torch.int32, device=device),
+                  "plan": torch.empty(int(plan_bytes.value), dtype=torch.uint8, device=device)}
+            self._exchange_state[key] = st
+        return st
+
+    def exchange_receive_set(self, st, device, key_dtype, val_dtype, capacity):
+        """The receive buffers of this call (alternating sets), (re)allocated when too small."""
+        i = st["turn"]
+        st["turn"] ^= 1
+        have = st["sets"][i]
+        if have is None or have[0].numel() < capacity:
+            k = torch.empty(capacity, dtype=key_dtype, device=device)
+            v = None if val_dtype is None else torch.empty(capacity, dtype=val_dtype, device=device)
+            st["sets"][i] = (k, v, self.export_buffer(k), None if v is None else self.export_buffer(v))
+            st["generation"][i] += 1
+        return i, st["sets"][i]
+
+    def exchange_hist(self, st, keys, descending, tag):
+        import ctypes as C
+        lib = api._lib.load()
+        api._check(lib.tb200_exchange_hist(api._ptr(keys), keys.numel(), api.DTYPE_CODE[keys.dtype], int(descending), C.c_ulonglong(tag),
+                                           api._ptr(st["row"]), api._stream()), "tb200_exchange_hist")
+        return st["row"]
+
+    def exchange_plan(self, st, rows, world, rank, key_dtype):
+        lib = api._lib.load()
+        api._check(lib.tb200_exchange_plan(api._ptr(rows), world, rank, api.DTYPE_CODE[key_dtype], api._ptr(st["plan"]), api._stream()),
+                   "tb200_exchange_plan")
+        return st["plan"]
+
+    def exchange_scatter(self, keys, vals, plan, dst_keys, dst_vals, descending):
+        import ctypes as C
+        m = len(dst_keys)
+        kp = (C.c_void_p * m)(*dst_keys)
+        vp = None if vals is None else (C.c_void_p * m)(*dst_vals)
+        api._call_with_ws("scatter", "tb200_exchange_scatter", api._ptr(keys), api._ptr(vals), keys.numel(), api.DTYPE_CODE[keys.dtype],
+                          0 if vals is None else vals.element_size(), int(descending), api._ptr(plan), m, kp, vp)
+
     _recv_cache = {}
 
     def receive_buffers(self, device, key_dtype, val_dtype, capacity):
@@ -168,12 +223,19 @@ def sharded_reduce(x_local, init, op="plus", group=None, ops=None):
     ops = ops or DeviceOps()
     init = np.asarray(init)
     acc = init.dtype
+    world, _ = _world(group)
     partial = ops.reduce(x_local, _NP_IDENTITY[op](acc)[()], op)
-    t = torch.from_numpy(np.asarray(partial, dtype=acc).reshape(1).copy()).to(x_local.device)
-    dist.all_reduce(_plumbing_view(t), op=_REDUCE_OP[op], group=group)
-    total = t.cpu().numpy().astype(acc)[0]
+    # The G partials are gathered bit for bit and folded on the host in the accumulator type: an
+    # all-reduce would compare unsigned partials as signed integers (the collective library has no
+    # unsigned min/max), and one word per rank costs the same either way.
+    mine = torch.from_numpy(np.asarray(partial, dtype=acc).reshape(1).copy()).to(x_local.device)
+    gathered = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather([_plumbing_view(g) for g in gathered], _plumbing_view(mine), group=group)
+    total = init
     with np.errstate(over="ignore"):
-        return _NP_OP[op](init, total).astype(acc)[()]
+        for g in gathered:
+            total = _NP_OP[op](total, g.cpu().numpy().view(acc)[0]).astype(acc)[()]
+    return total
 
 
 def sharded_scan(x_local, op="plus", exclusive=False, init=None, group=None, ops=None):
@@ -267,6 +329,67 @@ def _device_splitters(keys, n, world, descending, group, ops, samples_per_rank):
     return _plumbing_view(sample_keys)[pos].view(keys.dtype), gathered
 
 
+def _sort_by_histogram_exchange(keys, vals, descending, group, ops, mark):
+    """The default route of sharded_sort_by_key on GPUs: splitters from a 12-bit digit histogram.
+    One read of the shard builds the histogram; ONE all-gather gives every rank all histograms, from
+    which each derives the same plan (bin ranges per rank, its offsets into every receive buffer,
+    every rank's receive total); the host waits once, for ~400 bytes of that plan; one kernel per
+    GPU then stores every pair straight into its owner's receive buffer over NVLink; a collective
+    fences the stores; a stable local radix sort of what arrived finishes.  Returns None when some
+    receive buffer would overflow (heavily skewed keys): the caller then samples splitters instead.
+    The result is a view of a receive buffer that the call after next reuses."""
+    world, rank = _world(group)
+    dev = keys.device
+    n = keys.numel()
+    if n >= (1 << 30) or keys.element_size() not in (4, 8):
+        return None
+    vdt = None if vals is None else vals.dtype
+    st = ops.exchange_state(dev, keys.dtype, vdt)
+    capacity = int(1.25 * n) + 65536
+    which, (rk, rv, kexp, vexp) = ops.exchange_receive_set(st, dev, keys.dtype, vdt, capacity)
+    tag = (st["generation"][which] << 32) | rk.numel()
+    row = ops.exchange_hist(st, keys, descending, tag)
+    rows = torch.empty(world * st["row_words"], dtype=torch.int32, device=dev)
+    dist.all_gather_into_tensor(rows, row, group=group)
+    plan = ops.exchange_plan(st, rows, world, rank, keys.dtype)
+    mark("splitters")
+    head = plan[:st["head_bytes"]].cpu().numpy()                               # the one host wait
+    mark("host_wait")
+    table = head[8:].view(np.uint64).reshape(3, -1)                            # send_offset, recv_total, tag; 16 entries each
+    recv_total = table[1, :world].astype(np.int64)
+    tags = table[2, :world].copy()
+    caps = (tags & np.uint64(0xFFFFFFFF)).astype(np.int64)
+    if (recv_total > caps).any():
+        st["turn"] ^= 1                                                       # this set was not used
+        return None
+    if st["known_tags"][which] is None or not np.array_equal(st["known_tags"][which], tags):
+        # some rank (re)allocated this receive set: exchange the IPC handles (every rank sees the same tags and takes this branch together)
+        mine = np.concatenate([kexp[0], [kexp[1]], (vexp[0] if vexp else np.zeros(8, np.int64)), [vexp[1] if vexp else 0]]).astype(np.int64)
+        handles = _gather_rows(torch.from_numpy(mine).to(dev), world, group)
+        ptrs_k, ptrs_v = [], []
+        for d in range(world):
+            if d == rank:
+                ptrs_k.append(rk.data_ptr())
+                ptrs_v.append(None if rv is None else rv.data_ptr())
+            else:
+                ptrs_k.append(ops.open_buffer(handles[d, 0:8], int(handles[d, 8])))
+                ptrs_v.append(None if rv is None else ops.open_buffer(handles[d, 9:17], int(handles[d, 17])))
+        st["peer_ptrs"][which] = (ptrs_k, ptrs_v)
+        st["known_tags"][which] = tags
+    dst_k, dst_v = st["peer_ptrs"][which]
+    ops.exchange_scatter(keys, vals, plan, dst_k, dst_v, descending)
+    # every sender's stores must have landed before a receiver sorts its buffer
+    fence = torch.zeros(1, dtype=torch.int32, device=dev)
+    dist.all_reduce(fence, group=group)
+    mark("exchange")
+    m = int(recv_total[rank])
+    out_k = rk[:m]
+    out_v = None if rv is None else rv[:m]
+    ops.sort_by_key(out_k, out_v, descending)
+    mark("local_sort")
+    return out_k, out_v
+
+
 def _sort_by_scatter(keys, vals, descending, group, ops, samples_per_rank, mark):
     """The scatter route of sharded_sort_by_key; returns None if some receive buffer is too small
     (every rank takes the same decision from the same table)."""
@@ -326,7 +449,10 @@ def sharded_sort_by_key(keys_local, vals_local=None, descending=False, group=Non
     gather, all-gather of the samples, sort of the gathered sample and splitter pick, lower bounds,
     all-gather of the cut positions.  The host blocks once, to read the G x (G-1) cut positions that
     size the all-to-all; the merges after the exchange are enqueued without waiting again.
-    exchange: "scatter" (the default where available) does not sort first: it samples splitters from
+    exchange: "histogram" (the default on GPUs, see _sort_by_histogram_exchange) takes splitters from
+    a digit histogram of the unsorted shard: one collective, one short host wait, then the same
+    scatter kernel; its result is a view of a receive buffer that the call after next reuses.
+    "scatter" does not sort first either: it samples splitters from
     the unsorted shard, counts and exchanges bucket sizes, and then ONE kernel per GPU splits its
     pairs by key range and stores each pair straight into the owning GPU's receive buffer over
     NVLink (stable: source-rank-major, input order inside a source); a stable local radix sort of
@@ -343,6 +469,11 @@ def sharded_sort_by_key(keys_local, vals_local=None, descending=False, group=Non
     mark = (lambda label: stage_marks.append((label, stage_marks[0][1]()))) if stage_marks else (lambda label: None)
     world, rank = _world(group)
     can_peer = getattr(ops, "supports_peer_reads", False) and keys_local.is_cuda
+    if world > 1 and world <= 16 and keys_local.is_cuda and getattr(ops, "supports_histogram_exchange", False) and exchange in ("auto", "histogram"):
+        done = _sort_by_histogram_exchange(keys_local, vals_local, descending, group, ops, mark)
+        if done is not None:
+            return done
+        exchange = "scatter"                    # skewed keys: sampled splitters balance better
     if world > 1 and (exchange == "scatter" or (exchange == "auto" and can_peer and world <= 16)):
         done = _sort_by_scatter(keys_local, vals_local, descending, group, ops, samples_per_rank, mark)
         if done is not None:
@@ -467,3 +598,41 @@ def sharded_sort_by_key(keys_local, vals_local=None, descending=False, group=Non
         runs = nxt
     mark("merge")
     return runs[0]
+
+
+def check_sharded_sort(keys_out, vals_out, n_total, key_of_index, group=None, descending=False):
+    """Checks a sharded sort_by_key whose values were the original global indices 0 .. n_total-1 and
+    whose keys can be recomputed from an index (key_of_index: numpy index array -> numpy key array):
+    every output pair is an input pair; each shard is sorted, values increasing inside equal keys
+    (stable); shards are in rank order; the shard sizes add up and the values are, by count, sum and
+    sum of squares, the indices 0 .. n_total-1.  Together: the stable sort of the whole input.
+    Collective (every rank calls it); returns True on every rank or raises."""
+    world, rank = _world(group)
+    k = keys_out.cpu().numpy()
+    v = vals_out.cpu().numpy()
+    assert np.array_equal(key_of_index(v), k), "an output pair is not an input pair"
+    if k.size > 1:
+        a, b = (k[1:], k[:-1]) if not descending else (k[:-1], k[1:])
+        assert bool((a >= b).all()), "a shard is not sorted"
+        ties = k[1:] == k[:-1]
+        assert bool((v[1:][ties] > v[:-1][ties]).all()), "equal keys are not in input order"
+    v64 = v.astype(np.uint64)
+    with np.errstate(over="ignore"):
+        mine = np.array([k.size, int(v64.sum(dtype=np.uint64) & np.uint64(0x7FFFFFFFFFFFFFFF)),
+                         int((v64 * v64).sum(dtype=np.uint64) & np.uint64(0x7FFFFFFFFFFFFFFF)),
+                         int(k[0]) if k.size else -1, int(k[-1]) if k.size else -1,
+                         int(v[0]) if k.size else -1, int(v[-1]) if k.size else -1], dtype=np.int64)
+    rows = _gather_rows(torch.from_numpy(mine).to(keys_out.device), world, group)
+    assert int(rows[:, 0].sum()) == n_total, "shard sizes do not add up"
+    want1 = (n_total * (n_total - 1) // 2) % (1 << 63)                        # closed forms, modulo 2^63 like the sums above
+    want2 = ((n_total - 1) * n_total * (2 * n_total - 1) // 6) % (1 << 63)
+    with np.errstate(over="ignore"):
+        got1 = int(np.sum(rows[:, 1].astype(np.uint64), dtype=np.uint64) & np.uint64(0x7FFFFFFFFFFFFFFF))
+        got2 = int(np.sum(rows[:, 2].astype(np.uint64), dtype=np.uint64) & np.uint64(0x7FFFFFFFFFFFFFFF))
+    assert got1 == want1 and got2 == want2, "the values are not a permutation of the indices"
+    full = [r for r in range(world) if rows[r, 0] > 0]
+    for a, b in zip(full[:-1], full[1:]):
+        last, first = rows[a, 4], rows[b, 3]
+        assert (first >= last) if not descending else (first <= last), "shards are not in rank order"
+        assert first != last or rows[b, 5] > rows[a, 6], "equal keys across a shard boundary are not in input order"
+    return True
