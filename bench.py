@@ -2,6 +2,7 @@
 """Benchmark of the hot path: thrust::sort_by_key of 2^28 (uint32 key, uint32 value) pairs.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-extras]
+    python bench.py --case ALGO LOG2N [REPS]        (one algorithm, a few calls, for profilers)
 
 A step is one stable sort_by_key of the whole workload (uniform random 32-bit keys from seed 2,
 value = original index).  Rank 0 prints ONE JSON line:
@@ -314,6 +315,112 @@ def bench_others(torch, tb, lib, peak):
     return res
 
 
+def bench_sharded(torch, dist, sharded, dg, world, rank, peak, args):
+    """The other two sharded paths at N > 1, on the same terms as the sort: the 2^28-element
+    workloads of the reduce and scan configurations split across the ranks ("strong"), CUDA events
+    around the public call, max over ranks, results checked against values computed on the host.
+    reduce: per-GPU single-pass reduce, one all-gather of G accumulators, fold on the host (4 B/elem).
+    scan: per-GPU reduce, all-gather of G totals on the stream, carry folded on the device and read
+    by the scan kernels from device memory -- no host round trip; 12 B/elem by construction (the
+    shard is read twice), reported against the 8 B/elem of the single-GPU algorithm."""
+    n = 1 << 28
+    lo, hi = rank * n // world, (rank + 1) * n // world
+    res = []
+
+    def timed(fn, reps=10):
+        for _ in range(3):
+            fn()
+        dist.barrier()
+        torch.cuda.synchronize()
+        ts = time_calls(torch, fn, reps)
+        t = torch.tensor([float(np.median(ts))], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    hx = dg.reduce_input(hi - lo, start=lo)
+    x = torch.from_numpy(hx).cuda()
+    part = torch.tensor([int(hx.sum(dtype=np.int64))], device="cuda")
+    dist.all_reduce(part)
+    got = sharded.sharded_reduce(x, np.int64(0))
+    ok = int(got) == int(part.item())
+    ms = timed(lambda: sharded.sharded_reduce(x, np.int64(0)))
+    res.append({"name": "sharded reduce int32->int64 2^28", "ms": ms, "achieved_gbs": 4.0 * n / ms / 1e6, "frac_of_hbm_peak": 4.0 * n / ms / 1e6 / (peak * world),
+                "algorithmic_bytes_per_unit": 4, "verified": bool(ok)})
+    del x
+    hs = dg.scan_input_i32(hi - lo, start=lo)
+    s = torch.from_numpy(hs).cuda()
+    sums = torch.zeros(world, dtype=torch.int64, device="cuda")
+    sums[rank] = int(hs.sum(dtype=np.int64))
+    dist.all_reduce(sums)
+    before = int(sums[:rank].sum().item())
+    out = sharded.sharded_scan(s)
+    m32 = 1 << 32                                             # int32 sums wrap: compare modulo 2^32
+    ok = int(out[0]) % m32 == (before + int(hs[0])) % m32 and torch.equal(out[1:] - out[:-1], s[1:]) and \
+        int(out[-1]) % m32 == (before + int(hs.sum(dtype=np.int64))) % m32
+    flag = torch.tensor([1 if ok else 0], device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    ms = timed(lambda: sharded.sharded_scan(s))
+    res.append({"name": "sharded inclusive_scan int32 2^28", "ms": ms, "achieved_gbs": 8.0 * n / ms / 1e6, "frac_of_hbm_peak": 8.0 * n / ms / 1e6 / (peak * world),
+                "algorithmic_bytes_per_unit": 8, "bytes_moved_per_unit": 12, "verified": bool(flag.item())})
+    return res
+
+
+def run_case(args):
+    """`--case ALGO LOG2N [REPS]`: runs one hot-path algorithm a few times on its synthetic benchmark
+    input and exits -- the command that the profiler captures under profiles/ wrap, on a case small
+    enough for the profiler (a few hundred MB) yet larger than the 126 MB L2.
+    ALGO: reduce | scan | sort | sort64 | copy_if | partition_copy | unique | reduce_by_key | merge |
+    merge_sort | scan_by_key | unique_by_key | minmax."""
+    import torch
+    import thrust_b200 as tb
+    from thrust_b200 import datagen as dg
+    algo = args.case[0]
+    n = 1 << int(args.case[1])
+    reps = int(args.case[2]) if len(args.case) > 2 else 2
+    dev = lambda a: torch.from_numpy(a).cuda()  # noqa: E731
+    if algo == "reduce":
+        x = dev(dg.reduce_input(n))
+        run = lambda: tb.reduce(x, np.int64(0))  # noqa: E731
+    elif algo == "scan":
+        x = dev(dg.scan_input_i32(n))
+        run = lambda: tb.inclusive_scan(x)  # noqa: E731
+    elif algo in ("sort", "sort64"):
+        k0 = dev(dg.sort_keys_u32(n) if algo == "sort" else dg.sort_keys_u64_40bit(n))
+        v0 = torch.arange(n, dtype=torch.int32, device="cuda")
+        run = lambda: tb.sort_by_key(k0.clone(), v0.clone())  # noqa: E731
+    elif algo == "copy_if":
+        x = dev(dg.compaction_input(n))
+        run = lambda: tb.copy_if(x, "mod_eq", 2, 0)  # noqa: E731
+    elif algo == "partition_copy":
+        x = dev(dg.compaction_input(n))
+        run = lambda: tb.partition_copy(x, "mod_eq", 2, 0)  # noqa: E731
+    elif algo == "unique":
+        x = dev(dg.run_keys(n))
+        run = lambda: tb.unique_copy(x)  # noqa: E731
+    elif algo in ("reduce_by_key", "scan_by_key", "unique_by_key"):
+        k, v = dev(dg.run_keys(n)), dev(dg.run_values_f32(n))
+        run = {"reduce_by_key": lambda: tb.reduce_by_key(k, v), "scan_by_key": lambda: tb.inclusive_scan_by_key(k, v),
+               "unique_by_key": lambda: tb.unique_by_key_copy(k, v)}[algo]
+    elif algo == "minmax":
+        x = dev(dg.reduce_input(n))
+        run = lambda: tb.minmax_element(x)  # noqa: E731
+    elif algo == "merge":
+        a, b = dev(dg.merge_keys_u64(n, 4)), dev(dg.merge_keys_u64(n, 5))
+        va = torch.arange(n, dtype=torch.int32, device="cuda")
+        vb = va + n
+        run = lambda: tb.merge_by_key(a, b, va, vb)  # noqa: E731
+    elif algo == "merge_sort":
+        zk, zv = dg.zip_sort_input(n)
+        k0, v0 = dev(zk), dev(zv)
+        run = lambda: tb.merge_sort_by_key(k0.clone(), v0.clone())  # noqa: E731
+    else:
+        raise SystemExit("unknown algorithm " + algo)
+    for _ in range(reps):
+        run()
+    torch.cuda.synchronize()
+    print("done", algo, n)
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -485,6 +592,8 @@ def run_ours(args):
         "sort_roofline": {"algorithmic_bytes_per_key": 68, "achieved_gbs": 68.0 * N_KEYS / ms / 1e6, "frac_of_hbm_peak": 68.0 * N_KEYS / ms / 1e6 / peak / world},
     }
 
+    if world > 1:
+        line["sharded_others"] = bench_sharded(torch, dist, sharded, dg, world, rank, peak, args)
     if world == 1:
         del k, v, kalt, valt, ws, k0, v0
         torch.cuda.empty_cache()
@@ -516,7 +625,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--case", nargs="+", metavar=("ALGO", "LOG2N"), help="run one algorithm a few times for a profiler and exit (see run_case)")
     args = ap.parse_args()
+    if args.case:
+        return run_case(args)
     if args.impl == "reference":
         # a launcher may have pinned OpenMP to one thread for its ranks; the reference arm runs on rank 0
         # alone and is meant to use every host core (read when the oracle library loads its OpenMP runtime)

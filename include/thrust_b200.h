@@ -67,6 +67,16 @@ int tb200_inclusive_scan(const void* d_in, void* d_out, size_t n, int t, int op,
 int tb200_exclusive_scan(const void* d_in, void* d_out, size_t n, int t, int op,
                          const void* h_init, void* d_ws, size_t* ws_bytes, tb200_stream_t stream);
 
+/* The same two scans with the initial value in DEVICE memory (d_init: one element of type t, read
+ * when the kernels run, not when the call is made), so that a value produced by earlier work on the
+ * stream -- the carry of a multi-GPU scan -- never visits the host.  No counterpart in the
+ * reference.  tb200_inclusive_scan_dinit with d_init == NULL is tb200_inclusive_scan without init. */
+int tb200_inclusive_scan_dinit(const void* d_in, void* d_out, size_t n, int t, int op,
+                               const void* d_init, void* d_ws, size_t* ws_bytes, tb200_stream_t stream);
+int tb200_exclusive_scan_dinit(const void* d_in, void* d_out, size_t n, int t, int op,
+                               const void* d_init, void* d_ws, size_t* ws_bytes, tb200_stream_t stream);
+
+
 /* thrust::sort / stable_sort / sort_by_key / stable_sort_by_key with thrust::less (descending=0)
  * or thrust::greater (descending=1) on arithmetic keys -- thrust/system/cuda/detail/sort.h:
  * 1621-1754, radix path :1438-1508.  Stable.  Sorts d_keys (and d_vals) in place; d_keys_alt /

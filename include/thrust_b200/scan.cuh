@@ -28,7 +28,8 @@ template <class T> struct scan_tuning {
 
 template <class InIt, class OutIt, class T, class Op, bool INCLUSIVE, int VEC, int IPT>
 __global__ void __launch_bounds__(SCAN_BLOCK, 4)
-scan_kernel(InIt in, OutIt out, size_t n, T init, bool has_init, Op op, tile_state<T> ts, ws_header* hdr) {
+scan_kernel(InIt in, OutIt out, size_t n, T init, bool has_init, const T* init_ptr, Op op, tile_state<T> ts, ws_header* hdr) {
+  if (init_ptr) { init = *init_ptr; has_init = true; }   // an initial value that lives on the device (the carry of a sharded scan)
   constexpr int VPT = IPT / VEC;
   constexpr int NWARPS = SCAN_BLOCK / 32;
   constexpr int WCHUNK = 32 * IPT;
@@ -178,7 +179,8 @@ scan_chunk_reduce_kernel(const T* in, size_t n, size_t tiles, size_t tiles_per_c
 
 template <class T, class Op, bool INCLUSIVE, int VEC, int IPT>
 __global__ void __launch_bounds__(SCAN_BLOCK, SCAN2_CTAS_PER_SM)
-scan_chunk_kernel(const T* in, T* out, size_t n, size_t tiles, size_t tiles_per_chunk, T init, bool has_init, Op op, const T* partials) {
+scan_chunk_kernel(const T* in, T* out, size_t n, size_t tiles, size_t tiles_per_chunk, T init, bool has_init, const T* init_ptr, Op op, const T* partials) {
+  if (init_ptr) { init = *init_ptr; has_init = true; }
   constexpr int VPT = IPT / VEC;
   constexpr int NWARPS = SCAN_BLOCK / 32;
   constexpr int WCHUNK = 32 * IPT;
@@ -354,8 +356,9 @@ __device__ __forceinline__ vec16 load_l2_keep16(const void* p, unsigned long lon
 
 template <class T, class Op, bool INCLUSIVE, int VEC, int IPT>
 __global__ void __launch_bounds__(SCAN_BLOCK, SCANW_CTAS_PER_SM)
-scan_window_kernel(const T* in, T* out, size_t n, size_t tiles, unsigned tiles_per_chunk, T init, bool has_init, Op op, tile_state<T> ts,
-                   ws_header* hdr) {
+scan_window_kernel(const T* in, T* out, size_t n, size_t tiles, unsigned tiles_per_chunk, T init, bool has_init, const T* init_ptr, Op op,
+                   tile_state<T> ts, ws_header* hdr) {
+  if (init_ptr) { init = *init_ptr; has_init = true; }
   constexpr int VPT = IPT / VEC;
   constexpr int NWARPS = SCAN_BLOCK / 32;
   constexpr size_t WT = 32 * IPT;           // a warp's tile: each lane holds VPT 16-byte vectors, lane-interleaved
@@ -567,9 +570,10 @@ template <class T> size_t scan_workspace_bytes(size_t n) {
   return sizeof(ws_header) + need;   // every route fits
 }
 
-// Launches the scan on `stream`; no sync.  in == out is allowed.
+// Launches the scan on `stream`; no sync.  in == out is allowed.  d_init, if not null, points at an
+// initial value in device memory that replaces (init, has_init); it is read when the kernels run.
 template <bool INCLUSIVE, class InIt, class OutIt, class T, class Op>
-cudaError_t scan_async(InIt in, OutIt out, size_t n, T init, bool has_init, Op op, void* ws, cudaStream_t stream) {
+cudaError_t scan_async(InIt in, OutIt out, size_t n, T init, bool has_init, Op op, void* ws, cudaStream_t stream, const T* d_init = nullptr) {
   if (n == 0) return cudaMemsetAsync(ws, 0, sizeof(ws_header), stream);
   constexpr int IPT = scan_tuning<T>::IPT;
   const size_t tiles = (n + scan_tile_items<T>() - 1) / scan_tile_items<T>();
@@ -608,7 +612,7 @@ cudaError_t scan_async(InIt in, OutIt out, size_t n, T init, bool has_init, Op o
               cudaError_t e3 = cudaMemsetAsync(base, 0, sizeof(ws_header) + tile_state<T>::bytes(windows * grid), stream);
               if (e3 != cudaSuccess) return e3;
               timed_launch tl(KID_SCAN, stream);
-              kern<<<(unsigned)grid, SCAN_BLOCK, 0, stream>>>(in, out, n, tiles2, tpc, init, has_init, op, tsw, hdr);
+              kern<<<(unsigned)grid, SCAN_BLOCK, 0, stream>>>(in, out, n, tiles2, tpc, init, has_init, d_init, op, tsw, hdr);
               log_launch("scan_window_kernel", grid, SCAN_BLOCK, 0, n, stream);
               return cudaGetLastError();
             }
@@ -621,7 +625,7 @@ cudaError_t scan_async(InIt in, OutIt out, size_t n, T init, bool has_init, Op o
           if (e2 != cudaSuccess) return e2;
           timed_launch tl(KID_SCAN, stream);
           scan_chunk_reduce_kernel<T, Op, VEC, IPT2><<<(unsigned)chunks, SCAN_BLOCK, 0, stream>>>(in, n, tiles2, tiles_per_chunk, op, partials);
-          scan_chunk_kernel<T, Op, INCLUSIVE, VEC, IPT2><<<(unsigned)chunks, SCAN_BLOCK, 0, stream>>>(in, out, n, tiles2, tiles_per_chunk, init, has_init, op, partials);
+          scan_chunk_kernel<T, Op, INCLUSIVE, VEC, IPT2><<<(unsigned)chunks, SCAN_BLOCK, 0, stream>>>(in, out, n, tiles2, tiles_per_chunk, init, has_init, d_init, op, partials);
           log_launch("scan_chunk_reduce_kernel + scan_chunk_kernel", chunks, SCAN_BLOCK, 0, n, stream);
           return cudaGetLastError();
         }
@@ -644,13 +648,13 @@ cudaError_t scan_async(InIt in, OutIt out, size_t n, T init, bool has_init, Op o
     if constexpr (vec_ok) {
       if (vectors) {
         constexpr int VEC = 16 / sizeof(T);
-        scan_kernel<InIt, OutIt, T, Op, INCLUSIVE, VEC, IPT><<<(unsigned)tiles, SCAN_BLOCK, 0, stream>>>(in, out, n, init, has_init, op, ts, hdr);
+        scan_kernel<InIt, OutIt, T, Op, INCLUSIVE, VEC, IPT><<<(unsigned)tiles, SCAN_BLOCK, 0, stream>>>(in, out, n, init, has_init, d_init, op, ts, hdr);
         log_launch("scan_kernel (16-byte loads)", tiles, SCAN_BLOCK, 0, n, stream);
         return cudaGetLastError();
       }
     }
   }
-  scan_kernel<InIt, OutIt, T, Op, INCLUSIVE, 1, IPT><<<(unsigned)tiles, SCAN_BLOCK, 0, stream>>>(in, out, n, init, has_init, op, ts, hdr);
+  scan_kernel<InIt, OutIt, T, Op, INCLUSIVE, 1, IPT><<<(unsigned)tiles, SCAN_BLOCK, 0, stream>>>(in, out, n, init, has_init, d_init, op, ts, hdr);
   log_launch("scan_kernel (generic iterator)", tiles, SCAN_BLOCK, 0, n, stream);
   return cudaGetLastError();
 }

@@ -240,7 +240,7 @@ cudaError_t partition_finish_async(T* data, const T* scratch, size_t n, const vo
 // items land behind the kept ones in input order and the way back is a plain copy.
 template <class T, class Pred>
 cudaError_t partition_inplace_stream_async(T* data, T* scratch, size_t n, Pred pred, unsigned long long* d_count, void* ws, cudaStream_t stream) {
-  cudaError_t e = select_stream_async<false, true, T, Pred>((const T*)data, scratch, (T*)nullptr, n, pred, SELECT_REJ_BEHIND_SELECTED, d_count, ws, stream);
+cudaError_t e = select_stream_async<false, true, T, Pred>((const T*)data, scratch, (T*)nullptr, n, pred, SELECT_REJ_BEHIND_SELECTED, d_count, ws, stream);
   if (e != cudaSuccess) return e;
   return cudaMemcpyAsync(data, scratch, n * sizeof(T), cudaMemcpyDeviceToDevice, stream);
 }

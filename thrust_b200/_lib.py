@@ -20,6 +20,8 @@ PROTOTYPES = {
     "tb200_reduce": [_vp, _sz, _i, _i, _i, _vp, _vp, _vp, _szp, _vp],
     "tb200_inclusive_scan": [_vp, _vp, _sz, _i, _i, _vp, _vp, _szp, _vp],
     "tb200_exclusive_scan": [_vp, _vp, _sz, _i, _i, _vp, _vp, _szp, _vp],
+    "tb200_inclusive_scan_dinit": [_vp, _vp, _sz, _i, _i, _vp, _vp, _szp, _vp],
+    "tb200_exclusive_scan_dinit": [_vp, _vp, _sz, _i, _i, _vp, _vp, _szp, _vp],
     "tb200_sort_by_key": [_vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _vp, _szp, _vp],
     "tb200_copy_if": [_vp, _vp, _vp, _sz, _i, _i, _i, _ll, _ll, _vp, _vp, _szp, _vp],
     "tb200_partition_copy": [_vp, _vp, _vp, _vp, _sz, _i, _i, _i, _ll, _ll, _vp, _vp, _szp, _vp],

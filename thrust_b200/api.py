@@ -106,27 +106,48 @@ def reduce(x, init=None, op="plus", acc_dtype=None):
     return out.cpu().numpy().view(NP_OF[acc_dtype])[0]
 
 
-# ------------------------------------------------------------------------------------- scan
-def inclusive_scan(x, out=None, op="plus", init=None):
-    """thrust::inclusive_scan(first, last, result, op); out may be x (in place).  Returns out.
-    `init`, if given, is combined in front of the first element (the carry of a sharded scan)."""
-    _require_cuda(x, out)
-    out = torch.empty_like(x) if out is None else out
-    h_init = None if init is None else np.asarray(init, dtype=NP_OF[x.dtype])
-    ws = _call_with_ws("scan", "tb200_inclusive_scan", _ptr(x), _ptr(out), x.numel(), DTYPE_CODE[x.dtype], OPS[op],
-                       None if h_init is None else C.c_void_p(h_init.ctypes.data))
-    _sync_and_check(ws, "inclusive_scan")
+def reduce_to_device(x, init, op="plus", acc_dtype=None, out=None):
+    """The same reduction with the result left in device memory (a 1-element tensor of the accumulator
+    type) and nothing waited for: for callers that feed it to later work on the stream."""
+    _require_cuda(x)
+    acc_dtype = acc_dtype or x.dtype
+    h_init = np.asarray(init, dtype=NP_OF[acc_dtype])
+    out = torch.empty(1, dtype=acc_dtype, device=x.device) if out is None else out
+    _call_with_ws("reduce", "tb200_reduce", _ptr(x), x.numel(), DTYPE_CODE[x.dtype], DTYPE_CODE[acc_dtype], OPS[op],
+                  C.c_void_p(h_init.ctypes.data), _ptr(out))
     return out
 
 
-def exclusive_scan(x, init=0, out=None, op="plus"):
-    """thrust::exclusive_scan(first, last, result, init, op)."""
+# ------------------------------------------------------------------------------------- scan
+def inclusive_scan(x, out=None, op="plus", init=None, sync=True):
+    """thrust::inclusive_scan(first, last, result, op); out may be x (in place).  Returns out.
+    `init`, if given, is combined in front of the first element (the carry of a sharded scan): a
+    host scalar, or a 1-element CUDA tensor of x's type that earlier work on the stream fills in."""
     _require_cuda(x, out)
     out = torch.empty_like(x) if out is None else out
-    h_init = np.asarray(init, dtype=NP_OF[x.dtype])
-    ws = _call_with_ws("scan", "tb200_exclusive_scan", _ptr(x), _ptr(out), x.numel(), DTYPE_CODE[x.dtype], OPS[op],
-                       C.c_void_p(h_init.ctypes.data))
-    _sync_and_check(ws, "exclusive_scan")
+    if isinstance(init, torch.Tensor):
+        ws = _call_with_ws("scan", "tb200_inclusive_scan_dinit", _ptr(x), _ptr(out), x.numel(), DTYPE_CODE[x.dtype], OPS[op], _ptr(init))
+    else:
+        h_init = None if init is None else np.asarray(init, dtype=NP_OF[x.dtype])
+        ws = _call_with_ws("scan", "tb200_inclusive_scan", _ptr(x), _ptr(out), x.numel(), DTYPE_CODE[x.dtype], OPS[op],
+                           None if h_init is None else C.c_void_p(h_init.ctypes.data))
+    if sync:
+        _sync_and_check(ws, "inclusive_scan")
+    return out
+
+
+def exclusive_scan(x, init=0, out=None, op="plus", sync=True):
+    """thrust::exclusive_scan(first, last, result, init, op); init as for inclusive_scan."""
+    _require_cuda(x, out)
+    out = torch.empty_like(x) if out is None else out
+    if isinstance(init, torch.Tensor):
+        ws = _call_with_ws("scan", "tb200_exclusive_scan_dinit", _ptr(x), _ptr(out), x.numel(), DTYPE_CODE[x.dtype], OPS[op], _ptr(init))
+    else:
+        h_init = np.asarray(init, dtype=NP_OF[x.dtype])
+        ws = _call_with_ws("scan", "tb200_exclusive_scan", _ptr(x), _ptr(out), x.numel(), DTYPE_CODE[x.dtype], OPS[op],
+                           C.c_void_p(h_init.ctypes.data))
+    if sync:
+        _sync_and_check(ws, "exclusive_scan")
     return out
 
 

@@ -53,6 +53,11 @@ class DeviceOps:
     def exclusive_scan(self, x, op, init):
         return api.exclusive_scan(x, init=init, op=op)
 
+    carries_on_device = True
+
+    def reduce_to_device(self, x, identity, op):
+        return api.reduce_to_device(x, identity, op)
+
     def sort_by_key(self, keys, vals, descending):
         # enqueued only: the sharded algorithms wait for the GPU where they need a value on the host
         if vals is None:
@@ -244,6 +249,22 @@ def sharded_scan(x_local, op="plus", exclusive=False, init=None, group=None, ops
     ops = ops or DeviceOps()
     world, rank = _world(group)
     dt = _np_dtype(x_local)
+    if getattr(ops, "carries_on_device", False) and x_local.is_cuda and dist.get_backend(group) == "nccl":
+        # Nothing visits the host: the local total stays on the device, the all-gather runs on the
+        # stream, the totals of the ranks before this one are folded by the library's own reduce
+        # (seeded with init), and the scan reads its initial value from device memory.
+        ident = _NP_IDENTITY[op](dt)[()]
+        mine = ops.reduce_to_device(x_local, ident, op)
+        totals = torch.empty(world, dtype=x_local.dtype, device=x_local.device)
+        dist.all_gather_into_tensor(_plumbing_view(totals), _plumbing_view(mine), group=group)
+        seed = ident if init is None else np.asarray(init, dtype=dt)[()]
+        if rank == 0 and init is None:
+            carry = None if not exclusive else torch.from_numpy(np.zeros(1, dt)).to(x_local.device)
+        else:
+            carry = ops.reduce_to_device(totals[:rank], seed, op)
+        if exclusive:
+            return api.exclusive_scan(x_local, init=carry, op=op)
+        return api.inclusive_scan(x_local, op=op, init=carry)
     total = ops.reduce(x_local, _NP_IDENTITY[op](dt)[()], op)
     mine = torch.from_numpy(np.asarray(total, dtype=dt).reshape(1).copy()).to(x_local.device)
     gathered = [torch.empty_like(mine) for _ in range(world)]
