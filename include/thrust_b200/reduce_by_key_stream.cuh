@@ -44,14 +44,17 @@ template <class V, class Op> struct rbk_stream_combine {
 };
 
 // One row: the lane's keys and values, its head bits, and the pair of its own items.
-template <class K, class V, class Eq, class Op, int VEC>
+// FULL: the caller knows that the row lies wholly inside the input (no bounds checks).
+template <class K, class V, class Eq, class Op, int VEC, bool FULL = false>
 __device__ __forceinline__ rbk_stream_pair<V> rbk_stream_row(const K* keys, const V* vals, size_t n, size_t row, int lane, Eq eq, Op op, const K (&k)[VEC],
                                                             const V (&v)[VEC], K& prev_tail, bool& have_prev, unsigned& bits, unsigned& valid) {
-  bits = select_row_flags<true, K, Eq, VEC>(n, row, lane, eq, k, prev_tail, have_prev);
+  bits = select_row_flags<true, K, Eq, VEC, FULL>(n, row, lane, eq, k, prev_tail, have_prev);
   const size_t i0 = (row * 32 + lane) * VEC;
-  valid = 0;
+  valid = FULL ? (1u << VEC) - 1 : 0u;
+  if (!FULL) {
 #pragma unroll
-  for (int j = 0; j < VEC; ++j) if (i0 + j < n) valid |= 1u << j;
+    for (int j = 0; j < VEC; ++j) if (i0 + j < n) valid |= 1u << j;
+  }
   rbk_stream_pair<V> p;
   p.count = 0; p.value = v[0];
 #pragma unroll
@@ -121,23 +124,28 @@ rbk_stream_count_kernel(const K* keys, const V* vals, size_t n, size_t rows, siz
     const size_t first = batch * RBK_STREAM_ROWS;
     K prev_tail = K(); bool have_prev = false;
     select_batch_start(keys, first, VEC, prev_tail, have_prev);
-    K k[RBK_STREAM_ROWS][VEC];
-    V v[RBK_STREAM_ROWS][VEC];
-#pragma unroll
-    for (int u = 0; u < RBK_STREAM_ROWS; ++u)
-      if (first + u < rows) { select_row_load<K, VEC>(keys, n, first + u, lane, k[u]); select_row_load<V, VEC>(vals, n, first + u, lane, v[u]); }
     P acc; acc.count = 0; acc.value = V();
     bool have_acc = false;
+    // all batches but the last lie wholly inside the input: no bounds checks for them
+    auto body = [&](auto full_tag) {
+      constexpr bool FULL = decltype(full_tag)::value;
+      K k[RBK_STREAM_ROWS][VEC];
+      V v[RBK_STREAM_ROWS][VEC];
 #pragma unroll
-    for (int u = 0; u < RBK_STREAM_ROWS; ++u) {
-      if (first + u >= rows) break;
-      unsigned bits, valid;
-      P mine = rbk_stream_row<K, V, Eq, Op, VEC>(keys, vals, n, first + u, lane, eq, op, k[u], v[u], prev_tail, have_prev, bits, valid);
-      const rbk_stream_row_info<V> info = rbk_stream_row_scan<V, Op>(mine, (first + u + 1) * 32 * VEC <= n, valid != 0, lane, op);
-      P row_pair; row_pair.count = info.row_heads; row_pair.value = info.row_open;
-      acc = have_acc ? comb(acc, row_pair) : row_pair;
-      have_acc = true;
-    }
+      for (int u = 0; u < RBK_STREAM_ROWS; ++u)
+        if (FULL || first + u < rows) { select_row_load<K, VEC, FULL>(keys, n, first + u, lane, k[u]); select_row_load<V, VEC, FULL>(vals, n, first + u, lane, v[u]); }
+#pragma unroll
+      for (int u = 0; u < RBK_STREAM_ROWS; ++u) {
+        if (!FULL && first + u >= rows) break;
+        unsigned bits, valid;
+        P mine = rbk_stream_row<K, V, Eq, Op, VEC, FULL>(keys, vals, n, first + u, lane, eq, op, k[u], v[u], prev_tail, have_prev, bits, valid);
+        const rbk_stream_row_info<V> info = rbk_stream_row_scan<V, Op>(mine, FULL || (first + u + 1) * 32 * VEC <= n, valid != 0, lane, op);
+        P row_pair; row_pair.count = info.row_heads; row_pair.value = info.row_open;
+        acc = have_acc ? comb(acc, row_pair) : row_pair;
+        have_acc = true;
+      }
+    };
+    if ((first + RBK_STREAM_ROWS) * 32 * VEC <= n) body(std::true_type()); else body(std::false_type());
     if (lane == 0) batch_pairs[batch] = acc;
   }
 }
@@ -162,17 +170,19 @@ rbk_stream_emit_kernel(const K* keys, const V* vals, K* keys_out, V* vals_out, s
     if (batch > 0) carry = batch_incl[batch - 1];
     K prev_tail = K(); bool have_prev = false;
     select_batch_start(keys, first, VEC, prev_tail, have_prev);
+    auto body = [&](auto full_tag) {
+    constexpr bool FULL = decltype(full_tag)::value;
     K k[RBK_STREAM_ROWS][VEC];
     V v[RBK_STREAM_ROWS][VEC];
 #pragma unroll
     for (int u = 0; u < RBK_STREAM_ROWS; ++u)
-      if (first + u < rows) { select_row_load<K, VEC>(keys, n, first + u, lane, k[u]); select_row_load<V, VEC>(vals, n, first + u, lane, v[u]); }
+      if (FULL || first + u < rows) { select_row_load<K, VEC, FULL>(keys, n, first + u, lane, k[u]); select_row_load<V, VEC, FULL>(vals, n, first + u, lane, v[u]); }
 #pragma unroll
     for (int u = 0; u < RBK_STREAM_ROWS; ++u) {
-      if (first + u >= rows) break;
+      if (!FULL && first + u >= rows) break;
       unsigned bits, valid;
-      P mine = rbk_stream_row<K, V, Eq, Op, VEC>(keys, vals, n, first + u, lane, eq, op, k[u], v[u], prev_tail, have_prev, bits, valid);
-      const rbk_stream_row_info<V> info = rbk_stream_row_scan<V, Op>(mine, (first + u + 1) * 32 * VEC <= n, valid != 0, lane, op);
+      P mine = rbk_stream_row<K, V, Eq, Op, VEC, FULL>(keys, vals, n, first + u, lane, eq, op, k[u], v[u], prev_tail, have_prev, bits, valid);
+      const rbk_stream_row_info<V> info = rbk_stream_row_scan<V, Op>(mine, FULL || (first + u + 1) * 32 * VEC <= n, valid != 0, lane, op);
       P row_pair; row_pair.count = info.row_heads; row_pair.value = info.row_open;
       // second walk: at each head, the run before it is complete
       const unsigned long long row_first = carry.count;        // ordinal of the row's first head
@@ -206,6 +216,8 @@ rbk_stream_emit_kernel(const K* keys, const V* vals, K* keys_out, V* vals_out, s
       __syncwarp();
       carry = comb(carry, row_pair);
     }
+    };
+    if ((first + RBK_STREAM_ROWS) * 32 * VEC <= n) body(std::true_type()); else body(std::false_type());
     if (batch == batches - 1 && lane == 0) {
       // the last run ends with the input
       vals_out[carry.count - 1] = carry.value;
@@ -289,18 +301,20 @@ scan_by_key_stream_kernel(const K* keys, const V* vals, V* out, size_t n, size_t
     if (batch > 0) carry = batch_incl[batch - 1];
     K prev_tail = K(); bool have_prev = false;
     select_batch_start(keys, first, VEC, prev_tail, have_prev);
+    auto body = [&](auto full_tag) {
+    constexpr bool FULL = decltype(full_tag)::value;
     K k[RBK_STREAM_ROWS][VEC];
     V v[RBK_STREAM_ROWS][VEC];
 #pragma unroll
     for (int u = 0; u < RBK_STREAM_ROWS; ++u)
-      if (first + u < rows) { select_row_load<K, VEC>(keys, n, first + u, lane, k[u]); select_row_load<V, VEC>(vals, n, first + u, lane, v[u]); }
+      if (FULL || first + u < rows) { select_row_load<K, VEC, FULL>(keys, n, first + u, lane, k[u]); select_row_load<V, VEC, FULL>(vals, n, first + u, lane, v[u]); }
 #pragma unroll
     for (int u = 0; u < RBK_STREAM_ROWS; ++u) {
-      if (first + u >= rows) break;
+      if (!FULL && first + u >= rows) break;
       const size_t row = first + u;
-      const bool row_full = (row + 1) * 32 * VEC <= n;
+      const bool row_full = FULL || (row + 1) * 32 * VEC <= n;
       unsigned bits, valid;
-      P mine = rbk_stream_row<K, V, Eq, Op, VEC>(keys, vals, n, row, lane, eq, op, k[u], v[u], prev_tail, have_prev, bits, valid);
+      P mine = rbk_stream_row<K, V, Eq, Op, VEC, FULL>(keys, vals, n, row, lane, eq, op, k[u], v[u], prev_tail, have_prev, bits, valid);
       const rbk_stream_row_info<V> info = rbk_stream_row_scan<V, Op>(mine, row_full, valid != 0, lane, op);
       P row_pair; row_pair.count = info.row_heads; row_pair.value = info.row_open;
       // reduction of the run's items ahead of this lane's first item (meaningless if that item is a head)
@@ -330,6 +344,8 @@ scan_by_key_stream_kernel(const K* keys, const V* vals, V* out, size_t n, size_t
       }
       carry = comb(carry, row_pair);
     }
+    };
+    if ((first + RBK_STREAM_ROWS) * 32 * VEC <= n) body(std::true_type()); else body(std::false_type());
     if (batch == batches - 1 && lane == 0) hdr->error = scan_hdr->error;
   }
 }
