@@ -259,6 +259,21 @@ int tb200_bucket_scatter(const void* d_keys, const void* d_vals, size_t n, int k
                          const unsigned long long* h_dst_offsets, void* d_ws, size_t* ws_bytes,
                          tb200_stream_t stream);
 
+/* thrust::set_union / set_intersection / set_difference / set_symmetric_difference and their
+ * _by_key forms on sorted ranges -- thrust/system/cuda/detail/set_operations.h:1260-1760.
+ * op: 0 union, 1 intersection, 2 difference, 3 symmetric difference; multiset semantics as in the
+ * reference (an element occurring m times in A and n times in B: max(m, n), min(m, n), max(m - n, 0),
+ * |m - n| copies; where both sides contribute, A's copies come first).  Keys of type key_t (I32 U32
+ * I64 U64 F32 F64) sorted ascending (descending=1: descending); val_bytes 0, 4 or 8: values that
+ * travel with the kept keys (d_vals_b may be NULL for the intersection and the difference, which
+ * only keep A's).  The outputs must hold na + nb items (union, symmetric difference), na
+ * (difference) or min(na, nb) (intersection); the count goes to *d_count (device, may be NULL) and
+ * the workspace header.  na, nb < 2^32 - 1. */
+int tb200_set_operation(int op, const void* d_keys_a, size_t na, const void* d_keys_b, size_t nb,
+                        const void* d_vals_a, const void* d_vals_b, void* d_keys_out, void* d_vals_out,
+                        int key_t, int val_bytes, int descending, unsigned long long* d_count,
+                        void* d_ws, size_t* ws_bytes, tb200_stream_t stream);
+
 /* The same exchange with splitters taken from a digit histogram instead of a sorted sample: no
  * second pass over the keys, one collective, no sampling error.  No counterpart in the reference.
  *   tb200_exchange_sizes   words of one rank's histogram row, bytes of a plan, and bytes of the plan's

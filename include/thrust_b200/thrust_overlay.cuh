@@ -55,6 +55,7 @@
 #include "scan.cuh"
 #include "scan_by_key.cuh"
 #include "select.cuh"
+#include "set_ops.cuh"
 
 THRUST_NAMESPACE_BEGIN
 namespace cuda_cub {
@@ -614,6 +615,65 @@ thrust::pair<ItemsIt, ItemsIt> minmax_element(Policy& policy, ItemsIt first, Ite
 template <class Policy, class ItemsIt, tb200_overlay::enable_for<Policy> = 0>
 thrust::pair<ItemsIt, ItemsIt> minmax_element(Policy& policy, ItemsIt first, ItemsIt last) {
   return cuda_cub::minmax_element(policy, first, last, thrust::less<tb200_overlay::value_t<ItemsIt>>());
+}
+
+}  // namespace cuda_cub
+THRUST_NAMESPACE_END
+
+// ------------------------------------------------------------------------------------- set operations
+// replaces cuda_cub::set_union / set_intersection / set_difference / set_symmetric_difference and their
+// _by_key forms (thrust/system/cuda/detail/set_operations.h:1260-1760)
+THRUST_NAMESPACE_BEGIN
+namespace cuda_cub {
+namespace tb200_overlay {
+template <bool HAS_V, class Policy, class K1, class K2, class V1, class V2, class KO, class VO, class Comp>
+thrust::pair<KO, VO> set_any(Policy& policy, int op, K1 k1, K1 k1_last, K2 k2, K2 k2_last, V1 v1, V2 v2, KO ko, VO vo, Comp comp) {
+  using T = value_t<K1>;
+  const std::size_t na = (std::size_t)thrust::distance(k1, k1_last), nb = (std::size_t)thrust::distance(k2, k2_last);
+  scratch<Policy> tmp(policy, ::tb200::set_op_workspace_bytes(na, nb));
+  cudaError_t e = ::tb200::set_operation_async<T, HAS_V>(op, unwrap(k1), na, unwrap(k2), nb, unwrap(v1), unwrap(v2), unwrap(ko), unwrap(vo), comp, nullptr,
+                                                        tmp.at(), cuda_cub::stream(policy));
+  const std::size_t m = finish(policy, e, tmp.at(), "set operation failed");
+  return thrust::make_pair(ko + m, vo + m);
+}
+}  // namespace tb200_overlay
+
+#define TB200_SET_OPERATION(NAME, OP)                                                                                                         \
+  template <class Policy, class It1, class It2, class OutIt, class Comp, tb200_overlay::enable_for<Policy> = 0>                                \
+  OutIt NAME(Policy& policy, It1 first1, It1 last1, It2 first2, It2 last2, OutIt result, Comp comp) {                                          \
+    return tb200_overlay::set_any<false>(policy, OP, first1, last1, first2, last2, first1, first2, result, result, comp).first;                \
+  }                                                                                                                                            \
+  template <class Policy, class It1, class It2, class OutIt, tb200_overlay::enable_for<Policy> = 0>                                            \
+  OutIt NAME(Policy& policy, It1 first1, It1 last1, It2 first2, It2 last2, OutIt result) {                                                     \
+    return cuda_cub::NAME(policy, first1, last1, first2, last2, result, thrust::less<tb200_overlay::value_t<It1>>());                          \
+  }
+TB200_SET_OPERATION(set_union, ::tb200::SET_UNION)
+TB200_SET_OPERATION(set_intersection, ::tb200::SET_INTERSECTION)
+TB200_SET_OPERATION(set_difference, ::tb200::SET_DIFFERENCE)
+TB200_SET_OPERATION(set_symmetric_difference, ::tb200::SET_SYMMETRIC_DIFFERENCE)
+#undef TB200_SET_OPERATION
+
+#define TB200_SET_OPERATION_BY_KEY(NAME, OP)                                                                                                  \
+  template <class Policy, class K1, class K2, class V1, class V2, class KO, class VO, class Comp, tb200_overlay::enable_for<Policy> = 0>       \
+  thrust::pair<KO, VO> NAME(Policy& policy, K1 k1, K1 k1_last, K2 k2, K2 k2_last, V1 v1, V2 v2, KO ko, VO vo, Comp comp) {                     \
+    return tb200_overlay::set_any<true>(policy, OP, k1, k1_last, k2, k2_last, v1, v2, ko, vo, comp);                                           \
+  }                                                                                                                                            \
+  template <class Policy, class K1, class K2, class V1, class V2, class KO, class VO, tb200_overlay::enable_for<Policy> = 0>                   \
+  thrust::pair<KO, VO> NAME(Policy& policy, K1 k1, K1 k1_last, K2 k2, K2 k2_last, V1 v1, V2 v2, KO ko, VO vo) {                                \
+    return cuda_cub::NAME(policy, k1, k1_last, k2, k2_last, v1, v2, ko, vo, thrust::less<tb200_overlay::value_t<K1>>());                       \
+  }
+TB200_SET_OPERATION_BY_KEY(set_union_by_key, ::tb200::SET_UNION)
+TB200_SET_OPERATION_BY_KEY(set_difference_by_key, ::tb200::SET_DIFFERENCE)
+TB200_SET_OPERATION_BY_KEY(set_symmetric_difference_by_key, ::tb200::SET_SYMMETRIC_DIFFERENCE)
+#undef TB200_SET_OPERATION_BY_KEY
+// the intersection takes values from the first range only
+template <class Policy, class K1, class K2, class V1, class KO, class VO, class Comp, tb200_overlay::enable_for<Policy> = 0>
+thrust::pair<KO, VO> set_intersection_by_key(Policy& policy, K1 k1, K1 k1_last, K2 k2, K2 k2_last, V1 v1, KO ko, VO vo, Comp comp) {
+  return tb200_overlay::set_any<true>(policy, ::tb200::SET_INTERSECTION, k1, k1_last, k2, k2_last, v1, v1, ko, vo, comp);
+}
+template <class Policy, class K1, class K2, class V1, class KO, class VO, tb200_overlay::enable_for<Policy> = 0>
+thrust::pair<KO, VO> set_intersection_by_key(Policy& policy, K1 k1, K1 k1_last, K2 k2, K2 k2_last, V1 v1, KO ko, VO vo) {
+  return cuda_cub::set_intersection_by_key(policy, k1, k1_last, k2, k2_last, v1, ko, vo, thrust::less<tb200_overlay::value_t<K1>>());
 }
 
 }  // namespace cuda_cub

@@ -3,7 +3,8 @@
 oracle/ref_tests/Makefile compiles testing/<name>.cu of the reference (Thrust 1.14.0) -- its
 reduce, scan, sort, sort_by_key, stable_sort(_by_key), copy (copy_if), partition, unique,
 reduce_by_key, merge, merge_by_key tests and those of their callers (count, inner_product,
-transform_reduce, transform_scan, remove, extrema, scan_by_key, unique_by_key) -- against the CUDA
+transform_reduce, transform_scan, remove, extrema, scan_by_key, unique_by_key) and the set
+operations -- against the CUDA
 toolkit's Thrust with include/thrust_b200/thrust_overlay.cuh force-included, one executable each.
 The executables are built where the reference checkout is available and shipped as files; this
 test runs them and requires (1) exit code 0, i.e. every test case of the file passed, and (2) that
@@ -19,7 +20,9 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 BIN = os.path.join(ROOT, "oracle", "_ref", "tests")
 NAMES = ["reduce", "scan", "sort", "sort_by_key", "stable_sort", "stable_sort_by_key", "copy", "partition", "unique", "reduce_by_key",
          "merge", "merge_by_key", "count", "inner_product", "transform_reduce", "transform_scan", "remove", "min_element", "max_element",
-         "minmax_element", "scan_by_key", "unique_by_key"]
+         "minmax_element", "scan_by_key", "unique_by_key", "set_union", "set_union_by_key", "set_intersection", "set_intersection_by_key",
+         "set_difference", "set_difference_by_key", "set_symmetric_difference", "set_symmetric_difference_by_key", "set_union_descending",
+         "set_intersection_descending"]
 
 
 @pytest.mark.parametrize("name", NAMES)

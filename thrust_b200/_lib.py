@@ -38,6 +38,7 @@ PROTOTYPES = {
     "tb200_merge_runs": [_vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _szp, _vp],
     "tb200_bucket_count": [_vp, _sz, _i, _i, _vp, _i, _vp, _vp],
     "tb200_bucket_scatter": [_vp, _vp, _sz, _i, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _szp, _vp],
+    "tb200_set_operation": [_i, _vp, _sz, _vp, _sz, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _szp, _vp],
     "tb200_exchange_sizes": [_i, _szp, _szp, _szp],
     "tb200_exchange_hist": [_vp, _sz, _i, _i, C.c_ulonglong, _vp, _vp],
     "tb200_exchange_plan": [_vp, _i, _i, _i, _vp, _vp],

@@ -349,6 +349,31 @@ def merge(a, b, descending=False):
     return merge_by_key(a, b, None, None, descending)[0]
 
 
+SET_OPS = {"union": 0, "intersection": 1, "difference": 2, "symmetric_difference": 3}
+
+
+def set_operation(op, keys_a, keys_b, vals_a=None, vals_b=None, descending=False):
+    """thrust::set_union / set_intersection / set_difference / set_symmetric_difference (op names
+    as in SET_OPS) of two sorted ranges, and their _by_key forms when vals_a is given (vals_b for the
+    union and the symmetric difference, whose results also take items from B).  Returns
+    (keys_out, vals_out or None) cut to the result's length."""
+    _require_cuda(keys_a, keys_b, vals_a, vals_b)
+    if keys_a.dtype != keys_b.dtype:
+        raise ValueError("key types differ")
+    code = SET_OPS[op]
+    na, nb = keys_a.numel(), keys_b.numel()
+    cap = {0: na + nb, 1: min(na, nb), 2: na, 3: na + nb}[code]
+    ko = torch.empty(cap, dtype=keys_a.dtype, device=keys_a.device)
+    vo = None if vals_a is None else torch.empty(cap, dtype=vals_a.dtype, device=keys_a.device)
+    vb = 0 if vals_a is None else vals_a.element_size()
+    cnt = _count_word()
+    ws = _call_with_ws("setop", "tb200_set_operation", code, _ptr(keys_a), na, _ptr(keys_b), nb, _ptr(vals_a), _ptr(vals_b), _ptr(ko), _ptr(vo),
+                       DTYPE_CODE[keys_a.dtype], vb, int(descending), _ptr(cnt))
+    _sync_and_check(ws, "set_" + op)
+    m = _read_count(cnt)
+    return ko[:m], (None if vo is None else vo[:m])
+
+
 def merge_sort_by_key(keys, vals=None, descending=False):
     """The comparison-sort route of thrust::stable_sort(_by_key): stable merge sort in place."""
     _require_cuda(keys, vals)
