@@ -10,8 +10,12 @@ value = original index).  Rank 0 prints ONE JSON line:
   value        Gkeys/s with the inputs resident in HBM, CUDA-event time of the C-ABI call only
                (the pristine input is restored by a device copy between steps, outside the events;
                that 2 GiB copy also flushes L2);
-  e2e          the same metric through the host API with HOST buffers: pinned host -> device copy of
-               keys and values, sort, device -> pinned host copy of both, all inside the events;
+  e2e          the same metric through the host API with HOST buffers (thrust_b200.sort_by_key_host):
+               pinned host -> device copy of keys and values, sort, device -> pinned host copy of
+               both, all inside the events; the call sorts (key, position) pairs while the values
+               are still coming up and sends the sorted keys down meanwhile, so the two directions
+               of the host link overlap (N > 1: every rank copies its shard up, the sharded sort,
+               every rank copies its slice of the result down);
   roofline     the dominant kernel (one onesweep digit pass), timed live with CUDA events through
                the library's per-kernel timing switch: algorithmic bytes = 2 * (4 + 4) * n per pass;
   cpu_baseline the reference Thrust's OpenMP sort_by_key (oracle/_ref) on a bounded sample, N=1 only;
@@ -45,7 +49,7 @@ CPU_SAMPLE = 1 << 26
 FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes per onesweep launch per key, from the ncu capture summarised in
 # profiles/onesweep_u32_u32_2p25.md (dram read + write of one pass at 2^25 pairs, divided by 2^25)
-ONESWEEP_TRAFFIC_BYTES_PER_KEY = 14.85
+ONESWEEP_TRAFFIC_BYTES_PER_KEY = 14.47
 
 
 def hbm_peak():
@@ -550,12 +554,14 @@ def run_ours(args):
     h_out_v = torch.empty_like(h_vals).pin_memory()
     if world == 1:
         def e2e_step():
-            k.copy_(h_keys, non_blocking=True)
-            v.copy_(h_vals, non_blocking=True)
-            tb.sort_by_key(k, v)
-            h_out_k.copy_(k, non_blocking=True)
-            h_out_v.copy_(v, non_blocking=True)
+            tb.sort_by_key_host(h_keys, h_vals, h_out_k, h_out_v)
         d2h = 8 * n_local
+        e2e_api = ("thrust_b200.sort_by_key_host on pinned host tensors: keys up, (key, position) pairs sorted while the values follow on a second "
+                   "stream, sorted keys down while the values arrive, values permuted by position and sent down")
+        # the host-buffer call must give what the device call gave on the same data (k, v hold its result)
+        e2e_step()
+        if not (torch.equal(h_out_k.cuda(), k) and torch.equal(h_out_v.cuda(), v)):
+            raise SystemExit("sort_by_key_host disagrees with sort_by_key")
     else:
         dk, dv = torch.empty_like(k0), torch.empty_like(v0)
         # this rank's slice of the result is about n_local long; leave room for splitter imbalance
@@ -569,6 +575,7 @@ def run_ours(args):
             h_res_k[:rk.numel()].copy_(rk, non_blocking=True)
             h_res_v[:rv.numel()].copy_(rv, non_blocking=True)
         d2h = 8 * n_local
+        e2e_api = "thrust_b200.sharded.sharded_sort_by_key on shards filled from pinned host memory; every rank's slice of the result copied back to pinned host memory"
     e2e_step()
     barrier()
     e2e_times = time_calls(torch, e2e_step, max(1, min(args.steps, 3)))
@@ -579,7 +586,7 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
     e2e = {"value": N_KEYS / e2e_ms / 1e6, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": 8 * n_local, "d2h_bytes_per_step": d2h,
-           "api": "thrust_b200.sort_by_key on tensors filled from pinned host memory; result copied back to pinned host memory"}
+           "api": e2e_api}
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,

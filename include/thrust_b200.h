@@ -300,6 +300,18 @@ int tb200_exchange_scatter(const void* d_keys, const void* d_vals, size_t n, int
                            int descending, const void* d_plan, int ranks, void* const* h_dst_keys,
                            void* const* h_dst_vals, void* d_ws, size_t* ws_bytes, tb200_stream_t stream);
 
+/* Helpers of a sort_by_key whose keys and values start and end in host memory: the keys are sorted
+ * together with their positions (tb200_sequence_u32: d_out[i] = i, the job of thrust::sequence,
+ * thrust/system/cuda/detail/sequence.h / tabulate.h) while the values are still being copied to the
+ * device, and the values are then permuted by the sorted positions (tb200_gather:
+ * d_out[i] = d_src[d_index_u32[i]], the job of thrust::gather, thrust/system/cuda/detail/gather.h:
+ * 41-59), which lets the device-to-host copy of the sorted keys overlap the host-to-device copy of
+ * the values.  The result equals tb200_sort_by_key's (the sort is stable).  n <= 2^32 - 1;
+ * val_bytes 4 or 8; d_out of tb200_sequence_u32 16-byte aligned. */
+int tb200_sequence_u32(void* d_out, size_t n, tb200_stream_t stream);
+int tb200_gather(const void* d_src, const void* d_index_u32, void* d_out, size_t n, int val_bytes,
+                 tb200_stream_t stream);
+
 /* Sharing device buffers between the ranks of a one-process-per-GPU job, so that a kernel on one
  * GPU reads another GPU's buffer directly over NVLink with ordinary loads (the multi-GPU sort
  * merges the runs it needs straight out of its peers' memory instead of copying them first).
@@ -308,11 +320,15 @@ int tb200_exchange_scatter(const void* d_keys, const void* d_vals, size_t n, int
  *                      (cudaIpcGetMemHandle); send both to the peer process by any means;
  *   tb200_ipc_open     maps the peer's allocation into this process (once per handle; later calls
  *                      reuse the mapping) and returns the device pointer of the same bytes;
+ *   tb200_ipc_close    unmaps the allocation of one handle (every pointer tb200_ipc_open returned
+ *                      for it dies; a handle that is not open is not an error): call it when the
+ *                      peer is about to free or replace the buffer, after the work that used it;
  *   tb200_ipc_close_all unmaps everything opened so far.
  * The exporting process must keep the buffer allocated while peers use it, and the two sides
  * order their accesses themselves (a collective or a stream wait between writer and reader). */
 int tb200_ipc_export(const void* d_ptr, void* h_handle64, size_t* h_offset);
 int tb200_ipc_open(const void* h_handle64, size_t offset, void** d_ptr_out);
+int tb200_ipc_close(const void* h_handle64);
 int tb200_ipc_close_all(void);
 
 #ifdef __cplusplus

@@ -8,6 +8,7 @@
 #include <stdint.h>
 #include <stddef.h>
 #include <type_traits>
+#include <mutex>
 #include <new>
 #include <string.h>
 #include <stdio.h>
@@ -105,8 +106,11 @@ struct kernel_timer {
   int ids[CAP];
   cudaEvent_t start[CAP], stop[CAP];
   bool created[CAP] = {false};
+  std::mutex lock;                       // slots are handed out under it; calls may come from several host threads
   int begin(int id, cudaStream_t s) {
-    if (!enabled || used >= CAP) return -1;
+    if (!enabled) return -1;
+    std::lock_guard<std::mutex> guard(lock);
+    if (used >= CAP) return -1;
     int i = used++;
     if (!created[i]) { cudaEventCreate(&start[i]); cudaEventCreate(&stop[i]); created[i] = true; }
     ids[i] = id;

@@ -660,16 +660,33 @@ exchange_plan_kernel(const unsigned* rows, int ranks, int rank, int fields, exch
   __syncthreads();
   unsigned long long before = incl - sum, n_all = 0;
   for (int w = 0; w < 32; ++w) { if (w < warp) before += s_warp[w]; n_all += s_warp[w]; }
+  unsigned dest[4];
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const int b = threadIdx.x * 4 + j;
     unsigned long long d = n_all ? (before + mine[j]) * (unsigned long long)ranks / n_all : 0;   // the share in which the bin starts
     if (d > (unsigned long long)(ranks - 1)) d = ranks - 1;
+    dest[j] = (unsigned)d;
     s_dest[b] = (unsigned char)d;
     plan->lut[b] = (unsigned char)d;
-    for (int g = 0; g < ranks; ++g) {
-      const unsigned c = rows[(size_t)g * row_words + (size_t)field * EXCH_BINS + b];
-      if (c) atomicAdd(&s_cnt[g][d], (unsigned long long)c);
+  }
+  // [source][destination] counts.  Destinations grow with the bin, so nearly every warp's 128 bins
+  // go to one destination: such a warp adds its bins up with a shuffle reduction and issues one
+  // atomic per source; only the few warps that straddle a boundary add bin by bin.
+  const unsigned first_dest = __shfl_sync(FULL_MASK, dest[0], 0);           // every lane takes part: not inside a short-circuit
+  const bool warp_uniform = __all_sync(FULL_MASK, (dest[0] == dest[3]) & (dest[0] == first_dest));
+  for (int g = 0; g < ranks; ++g) {
+    const uint4 c = *reinterpret_cast<const uint4*>(rows + (size_t)g * row_words + (size_t)field * EXCH_BINS + threadIdx.x * 4);
+    if (warp_uniform) {
+      unsigned long long t = (unsigned long long)c.x + c.y + c.z + c.w;
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) t += __shfl_xor_sync(FULL_MASK, t, d);
+      if (lane == 0 && t) atomicAdd(&s_cnt[g][dest[0]], t);
+    } else {
+      if (c.x) atomicAdd(&s_cnt[g][dest[0]], (unsigned long long)c.x);
+      if (c.y) atomicAdd(&s_cnt[g][dest[1]], (unsigned long long)c.y);
+      if (c.z) atomicAdd(&s_cnt[g][dest[2]], (unsigned long long)c.z);
+      if (c.w) atomicAdd(&s_cnt[g][dest[3]], (unsigned long long)c.w);
     }
   }
   __syncthreads();

@@ -12,6 +12,7 @@ namespace tb200 {
 
 constexpr int REDUCE_BLOCK = 256;
 constexpr int REDUCE_UNROLL = 4;
+constexpr int REDUCE_UNROLL_GENERIC = 16;
 constexpr int REDUCE_CTAS_PER_SM = 4;
 constexpr int REDUCE_MAX_GRID = 4096;
 
@@ -70,13 +71,18 @@ reduce_kernel(InIt in, size_t n, AccT init, Op op, AccT* partials, unsigned* par
     size_t t = nvec * VEC + tid;
     if (t < n) acc.append((AccT)in[t], op);
   } else {
+    // one element per load: sixteen of them in flight per thread keep as many bytes on their way as
+    // the four 16-byte loads of the vector path (a transform_iterator over 4-byte items, say)
+    constexpr int U = REDUCE_UNROLL_GENERIC;
     size_t i = tid;
-    for (; i + (REDUCE_UNROLL - 1) * stride < n; i += REDUCE_UNROLL * stride) {
-      AccT r[REDUCE_UNROLL];
+    for (; i + (U - 1) * stride < n; i += U * stride) {
+      AccT r[U];
 #pragma unroll
-      for (int u = 0; u < REDUCE_UNROLL; ++u) r[u] = (AccT)in[i + u * stride];
+      for (int u = 0; u < U; ++u) r[u] = (AccT)in[i + u * stride];
+      AccT t = r[0];
 #pragma unroll
-      for (int u = 0; u < REDUCE_UNROLL; ++u) acc.append(r[u], op);
+      for (int u = 1; u < U; ++u) t = op(t, r[u]);
+      acc.append(t, op);
     }
     for (; i < n; i += stride) acc.append((AccT)in[i], op);
   }

@@ -46,6 +46,7 @@
 
 #include <cstdint>
 #include <type_traits>
+#include <vector>
 
 #include "extrema.cuh"
 #include "merge.cuh"
@@ -115,13 +116,87 @@ template <class K> struct radix_key {
 // number of algorithm calls this overlay has served in this process (lets a caller verify that it is active)
 inline unsigned long long& call_count() { static unsigned long long c = 0; return c; }
 
+// Temporary storage.  A policy that carries an allocator takes it from that allocator, through
+// thrust::detail::temporary_array, as in the reference (thrust/system/cuda/detail/par.h:86-108).
+// The other policies would pay a cudaMalloc and a cudaFree per call there (reduce.h:959), several
+// times the cost of reducing a gigabyte; for them each host thread keeps one buffer per (device,
+// stream), grown on demand and released when the thread ends.  Calls of one thread on one stream
+// are ordered on that stream, so they can share it.  -DTHRUST_B200_NO_SCRATCH_CACHE restores the
+// allocation per call.
+template <class P> struct has_allocator : std::false_type {};
+template <class Alloc, template <class> class Base> struct has_allocator<thrust::detail::execute_with_allocator<Alloc, Base>> : std::true_type {};
+
+struct scratch_cache {
+  struct entry { int device; cudaStream_t stream; void* p; std::size_t bytes; bool busy; };
+  std::vector<entry> entries;
+  ~scratch_cache() { for (entry& e : entries) if (e.p) cudaFree(e.p); }            // errors at process exit are not reported
+  // the (device, stream) buffer of at least `bytes`, marked busy; nullptr if a call further up the
+  // stack of this thread is using it (the caller then allocates for itself)
+  void* acquire(cudaStream_t stream, std::size_t bytes, std::size_t& slot) {
+    int device = 0;
+    cuda_cub::throw_on_error(cudaGetDevice(&device), "temporary storage: no current device");
+    entry* hit = nullptr;
+    for (entry& e : entries) if (e.device == device && e.stream == stream) { hit = &e; break; }
+    if (!hit) { entries.push_back(entry{device, stream, nullptr, 0, false}); hit = &entries.back(); }
+    if (hit->busy) return nullptr;
+    slot = (std::size_t)(hit - entries.data());
+    if (hit->bytes < bytes) {
+      if (hit->p) {                                                                  // earlier work on the stream may still use it
+        cuda_cub::throw_on_error(cudaStreamSynchronize(stream), "temporary storage: failed to synchronize");
+        cuda_cub::throw_on_error(cudaFree(hit->p), "temporary storage: free failed");
+        hit->p = nullptr; hit->bytes = 0;
+      }
+      const std::size_t want = bytes + bytes / 4;
+      cuda_cub::throw_on_error(cudaMalloc(&hit->p, want), "temporary storage: allocation failed");
+      hit->bytes = want;
+    }
+    hit->busy = true;
+    return hit->p;
+  }
+  void release(std::size_t slot) { entries[slot].busy = false; }
+};
+inline scratch_cache& thread_scratch_cache() { static thread_local scratch_cache c; return c; }
+
+#ifdef THRUST_B200_NO_SCRATCH_CACHE
+template <class Policy, bool FROM_POLICY = true> struct scratch;
+#else
+template <class Policy, bool FROM_POLICY = has_allocator<Policy>::value> struct scratch;
+#endif
 // workspace + result read-back shared by all wrappers
-template <class Policy> struct scratch {
+template <class Policy> struct scratch<Policy, true> {
   thrust::detail::temporary_array<std::uint8_t, Policy> storage;
   scratch(Policy& policy, std::size_t bytes) : storage(policy, bytes + 256) { ++call_count(); }
   std::uint8_t* at(std::size_t offset = 0) {
     std::uint8_t* p = thrust::raw_pointer_cast(storage.data());
     std::uintptr_t a = (reinterpret_cast<std::uintptr_t>(p) + 255) & ~std::uintptr_t(255);
+    return reinterpret_cast<std::uint8_t*>(a) + offset;
+  }
+};
+template <class Policy> struct scratch<Policy, false> {
+  std::uint8_t* base;
+  std::size_t slot = 0;
+  bool own = false;                                    // a nested call: allocated here, freed here
+  scratch(Policy& policy, std::size_t bytes) {
+    ++call_count();
+    // requests above 256 MiB (the alternate buffers of a large sort) are not worth keeping: the
+    // allocation is small beside the work, and the memory would stay with the thread
+    base = bytes > (std::size_t(256) << 20) ? nullptr
+                                            : static_cast<std::uint8_t*>(thread_scratch_cache().acquire(cuda_cub::stream(policy), bytes + 256, slot));
+    if (!base) {
+      void* p = nullptr;
+      cuda_cub::throw_on_error(cudaMalloc(&p, bytes + 256), "temporary storage: allocation failed");
+      base = static_cast<std::uint8_t*>(p);
+      own = true;
+    }
+  }
+  scratch(const scratch&) = delete;
+  scratch& operator=(const scratch&) = delete;
+  ~scratch() {
+    if (own) cudaFree(base);                           // synchronises with the work that used it
+    else thread_scratch_cache().release(slot);
+  }
+  std::uint8_t* at(std::size_t offset = 0) {
+    std::uintptr_t a = (reinterpret_cast<std::uintptr_t>(base) + 255) & ~std::uintptr_t(255);
     return reinterpret_cast<std::uint8_t*>(a) + offset;
   }
 };

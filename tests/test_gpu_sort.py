@@ -196,3 +196,20 @@ def test_full_size_stable_sort_zip_both_routes(tb):
         _sorted_permutation_stable(k0, k, v, None)
         outs.append((k, v))
     assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+
+
+@pytest.mark.parametrize("n", [0, 1, 4097, 200003, (1 << 22) + 5])
+def test_sort_by_key_host_buffers_match_the_oracle(tb, port, n):
+    """The host-buffer call (keys and values in pinned host memory; values permuted by the sorted
+    positions) gives exactly what the reference's stable sort_by_key gives, ties included."""
+    for kdt, vdt, desc in ((np.uint32, np.uint32, False), (np.float32, np.int64, True), (np.int64, np.float32, False)):
+        k = rand_of(kdt, n, 77, small=(kdt == np.int64))          # small: many equal keys, so stability shows
+        v = rand_of(vdt, n, 78)
+        hk, hv = torch.from_numpy(k.copy()).pin_memory(), torch.from_numpy(v.copy()).pin_memory()
+        ok_, ov_ = torch.empty_like(hk).pin_memory(), torch.empty_like(hv).pin_memory()
+        tb.sort_by_key_host(hk, hv, ok_, ov_, descending=desc)
+        wk, wv = port.sort_by_key(k, v, descending=desc)
+        assert np.array_equal(ok_.numpy().view(np.uint8), wk.view(np.uint8)) and np.array_equal(ov_.numpy().view(np.uint8), wv.view(np.uint8)), (kdt, n)
+        assert np.array_equal(hk.numpy().view(np.uint8), k.view(np.uint8))             # inputs untouched when outputs are given
+        tb.sort_by_key_host(hk, hv, descending=desc)                                   # in place
+        assert np.array_equal(hk.numpy().view(np.uint8), wk.view(np.uint8)) and np.array_equal(hv.numpy().view(np.uint8), wv.view(np.uint8))

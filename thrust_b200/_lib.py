@@ -49,7 +49,10 @@ PROTOTYPES = {
     "tb200_inclusive_scan_static_status": [_vp, C.POINTER(C.c_uint)],
     "tb200_ipc_export": [_vp, _vp, _szp],
     "tb200_ipc_open": [_vp, _sz, C.POINTER(C.c_void_p)],
+    "tb200_ipc_close": [_vp],
     "tb200_ipc_close_all": [],
+    "tb200_sequence_u32": [_vp, _sz, _vp],
+    "tb200_gather": [_vp, _vp, _vp, _sz, _i, _vp],
     "tb200_kernel_timing": [_i],
     "tb200_kernel_timing_read": [_i, C.POINTER(C.c_int), C.POINTER(C.c_float), C.POINTER(C.c_int)],
 }

@@ -186,6 +186,55 @@ def sort_by_key(keys, vals, descending=False, begin_bit=0, end_bit=None, sync=Tr
 
 stable_sort_by_key = sort_by_key
 
+_side_streams = {}
+
+
+def sort_by_key_host(h_keys, h_vals, h_keys_out=None, h_vals_out=None, descending=False):
+    """thrust::sort_by_key for keys and values that start and end in (pinned) host memory: the call
+    a host-side caller makes when the data does not live on the device.  The keys go up first and are
+    sorted together with their positions while the values are still on their way up on a second
+    stream; the sorted keys then travel back down while the values finish arriving (PCIe carries
+    both directions at once), the values are permuted by the sorted positions (tb200_gather) and
+    follow.  The result equals sort_by_key's on the same data (the sort is stable).  h_*_out default
+    to the inputs (in place).  Returns (h_keys_out, h_vals_out) after synchronising."""
+    if h_keys.is_cuda or h_vals.is_cuda:
+        raise ValueError("sort_by_key_host takes host tensors; device tensors go to sort_by_key")
+    n = h_keys.numel()
+    if h_vals.numel() != n or h_vals.element_size() not in (4, 8) or n > 0xFFFFFFFF:
+        raise ValueError("need one 4- or 8-byte value per key and at most 2^32 - 1 pairs")
+    h_keys_out = h_keys if h_keys_out is None else h_keys_out
+    h_vals_out = h_vals if h_vals_out is None else h_vals_out
+    if n == 0:
+        return h_keys_out, h_vals_out
+    lib = _lib.load()
+    dev = torch.cuda.current_device()
+    main = torch.cuda.current_stream()
+    side = _side_streams.get(dev)
+    if side is None:
+        side = _side_streams[dev] = torch.cuda.Stream()
+    vb = h_vals.element_size()
+    d_keys = workspaces.get("host_sort_keys", n * h_keys.element_size()).view(h_keys.dtype)[:n]
+    d_pos = workspaces.get("host_sort_pos", n * 4).view(torch.int32)[:n]
+    d_vals = workspaces.get("host_sort_vals", n * vb).view(h_vals.dtype)[:n]
+    d_vals_out = workspaces.get("host_sort_vals_out", n * vb).view(h_vals.dtype)[:n]
+    d_keys.copy_(h_keys.view(-1), non_blocking=True)
+    keys_up = torch.cuda.Event()
+    keys_up.record(main)
+    side.wait_stream(main)                              # the value buffer may still be read by an earlier call's gather
+    with torch.cuda.stream(side):
+        side.wait_event(keys_up)                        # keys first: the sort can start while the values follow
+        d_vals.copy_(h_vals.view(-1), non_blocking=True)
+        vals_up = torch.cuda.Event()
+        vals_up.record(side)
+    _check(lib.tb200_sequence_u32(_ptr(d_pos), n, _stream()), "tb200_sequence_u32")
+    sort_by_key(d_keys, d_pos, descending, sync=False)
+    h_keys_out.view(-1).copy_(d_keys, non_blocking=True)
+    main.wait_event(vals_up)
+    _check(lib.tb200_gather(_ptr(d_vals), _ptr(d_pos), _ptr(d_vals_out), n, vb, _stream()), "tb200_gather")
+    h_vals_out.view(-1).copy_(d_vals_out, non_blocking=True)
+    _sync_and_check(workspaces.get("sort", 1), "sort_by_key_host")      # waits for the stream
+    return h_keys_out, h_vals_out
+
 
 # ------------------------------------------------------------------------------------- compaction
 def _count_word():

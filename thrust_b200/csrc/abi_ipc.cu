@@ -68,6 +68,17 @@ TB200_API int tb200_ipc_open(const void* h_handle64, size_t offset, void** d_ptr
   return 0;
 }
 
+TB200_API int tb200_ipc_close(const void* h_handle64) {
+  if (!h_handle64) return ERR_INVALID;
+  std::string key(static_cast<const char*>(h_handle64), 64);
+  std::lock_guard<std::mutex> guard(g_lock);
+  auto it = g_open.find(key);
+  if (it == g_open.end()) return 0;                       // never opened here, or closed already
+  cudaError_t e = cudaIpcCloseMemHandle(it->second.base);
+  g_open.erase(it);
+  return (int)e;
+}
+
 TB200_API int tb200_ipc_close_all(void) {
   std::lock_guard<std::mutex> guard(g_lock);
   int rc = 0;

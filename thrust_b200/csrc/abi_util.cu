@@ -5,6 +5,7 @@ using namespace tb200_abi;
 
 TB200_API int tb200_kernel_timing(int enable) {
   tb200::kernel_timer& t = tb200::global_kernel_timer();
+  std::lock_guard<std::mutex> guard(t.lock);
   t.enabled = enable != 0;
   t.used = 0;
   return 0;
@@ -13,6 +14,7 @@ TB200_API int tb200_kernel_timing(int enable) {
 TB200_API int tb200_kernel_timing_read(int capacity, int* h_kernel_ids, float* h_ms, int* h_count) {
   if (!h_kernel_ids || !h_ms || !h_count || capacity < 0) return ERR_INVALID;
   tb200::kernel_timer& t = tb200::global_kernel_timer();
+  std::lock_guard<std::mutex> guard(t.lock);
   int n = t.used < capacity ? t.used : capacity;
   for (int i = 0; i < n; ++i) {
     cudaError_t e = cudaEventSynchronize(t.stop[i]);

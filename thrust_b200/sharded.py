@@ -55,8 +55,8 @@ class DeviceOps:
 
     carries_on_device = True
 
-    def reduce_to_device(self, x, identity, op):
-        return api.reduce_to_device(x, identity, op)
+    def reduce_to_device(self, x, identity, op, acc_dtype=None):
+        return api.reduce_to_device(x, identity, op, acc_dtype=acc_dtype)
 
     def sort_by_key(self, keys, vals, descending):
         # enqueued only: the sharded algorithms wait for the GPU where they need a value on the host
@@ -87,6 +87,12 @@ class DeviceOps:
         out = C.c_void_p(0)
         api._check(lib.tb200_ipc_open(C.c_void_p(h.ctypes.data), int(offset), C.byref(out)), "tb200_ipc_open")
         return int(out.value)
+
+    def close_buffer(self, handle):
+        """Unmaps a peer's buffer (every pointer open_buffer returned for this handle dies)."""
+        import ctypes as C
+        h = np.ascontiguousarray(handle, dtype=np.int64)
+        api._check(api._lib.load().tb200_ipc_close(C.c_void_p(h.ctypes.data)), "tb200_ipc_close")
 
     def merge_by_key_raw(self, ka, na, kb, nb, va, vb, key_dtype, val_dtype, descending, device):
         """merge_by_key on raw device pointers (which may point into a peer GPU's memory)."""
@@ -134,6 +140,7 @@ class DeviceOps:
             words, plan_bytes, head = C.c_size_t(0), C.c_size_t(0), C.c_size_t(0)
             api._check(lib.tb200_exchange_sizes(api.DTYPE_CODE[key_dtype], C.byref(words), C.byref(plan_bytes), C.byref(head)), "tb200_exchange_sizes")
             st = {"sets": [None, None], "generation": [0, 0], "turn": 0, "known_tags": [None, None], "peer_ptrs": [None, None],
+                  "peer_handles": [set(), set()],
                   "row_words": int(words.value), "plan_bytes": int(plan_bytes.value), "head_bytes": int(head.value),
                   "row": torch.empty(int(words.value), dtype=torch.int32, device=device),
                   "plan": torch.empty(int(plan_bytes.value), dtype=torch.uint8, device=device)}
@@ -229,10 +236,20 @@ def sharded_reduce(x_local, init, op="plus", group=None, ops=None):
     init = np.asarray(init)
     acc = init.dtype
     world, _ = _world(group)
-    partial = ops.reduce(x_local, _NP_IDENTITY[op](acc)[()], op)
     # The G partials are gathered bit for bit and folded on the host in the accumulator type: an
     # all-reduce would compare unsigned partials as signed integers (the collective library has no
     # unsigned min/max), and one word per rank costs the same either way.
+    if getattr(ops, "carries_on_device", False) and x_local.is_cuda and dist.get_backend(group) == "nccl":
+        # the partial never leaves the device before the gather: one host wait in all
+        mine = ops.reduce_to_device(x_local, _NP_IDENTITY[op](acc)[()], op, acc_dtype=api.TORCH_OF[np.dtype(acc)])
+        gathered = torch.empty(world, dtype=mine.dtype, device=x_local.device)
+        dist.all_gather_into_tensor(_plumbing_view(gathered), _plumbing_view(mine), group=group)
+        total = init
+        with np.errstate(over="ignore"):
+            for g in gathered.cpu().numpy().view(acc):
+                total = _NP_OP[op](total, g).astype(acc)[()]
+        return total
+    partial = ops.reduce(x_local, _NP_IDENTITY[op](acc)[()], op)
     mine = torch.from_numpy(np.asarray(partial, dtype=acc).reshape(1).copy()).to(x_local.device)
     gathered = [torch.empty_like(mine) for _ in range(world)]
     dist.all_gather([_plumbing_view(g) for g in gathered], _plumbing_view(mine), group=group)
@@ -387,6 +404,21 @@ def _sort_by_histogram_exchange(keys, vals, descending, group, ops, mark):
         # some rank (re)allocated this receive set: exchange the IPC handles (every rank sees the same tags and takes this branch together)
         mine = np.concatenate([kexp[0], [kexp[1]], (vexp[0] if vexp else np.zeros(8, np.int64)), [vexp[1] if vexp else 0]]).astype(np.int64)
         handles = _gather_rows(torch.from_numpy(mine).to(dev), world, group)
+        # the peers' previous buffers of this set are gone (or about to be): unmap the ones that are not
+        # among the new handles or the other set's.  Nothing of this process is still writing into
+        # them: the last scatter into this set was two calls ago and a fence followed it.
+        fresh = set()
+        for d in range(world):
+            if d != rank:
+                fresh.add(handles[d, 0:8].astype(np.int64).tobytes())
+                if rv is not None:
+                    fresh.add(handles[d, 9:17].astype(np.int64).tobytes())
+        stale = st["peer_handles"][which] - fresh - st["peer_handles"][which ^ 1]
+        if stale:
+            torch.cuda.current_stream().synchronize()
+            for hb in stale:
+                ops.close_buffer(np.frombuffer(hb, dtype=np.int64))
+        st["peer_handles"][which] = fresh
         ptrs_k, ptrs_v = [], []
         for d in range(world):
             if d == rank:
@@ -568,6 +600,7 @@ def sharded_sort_by_key(keys_local, vals_local=None, descending=False, group=Non
         ksz = keys.element_size()
         vsz = 0 if vals is None else vals.element_size()
         runs = []
+        opened = set()
         for src in range(world):
             start = int(bounds[src, rank])
             cnt = int(count_matrix[src, rank])
@@ -577,6 +610,9 @@ def sharded_sort_by_key(keys_local, vals_local=None, descending=False, group=Non
             else:
                 kp = ops.open_buffer(handles[src, 0:8], int(handles[src, 8]))
                 vp = None if vals is None else ops.open_buffer(handles[src, 9:17], int(handles[src, 17]))
+                opened.add(handles[src, 0:8].astype(np.int64).tobytes())
+                if vals is not None:
+                    opened.add(handles[src, 9:17].astype(np.int64).tobytes())
             runs.append((kp + start * ksz, None if vp is None else vp + start * vsz, cnt, None))
         mark("exchange")
         vdtype = None if vals is None else vals.dtype
@@ -600,6 +636,12 @@ def sharded_sort_by_key(keys_local, vals_local=None, descending=False, group=Non
         fence = torch.zeros(1, dtype=torch.int32, device=dev)
         dist.all_reduce(fence, group=group)
         mark("merge")
+        # the shards were the callers' own tensors, which they may free or reuse at any time: unmap
+        # them once this rank's merges have read them (a stale mapping must never be served again)
+        if hasattr(ops, "close_buffer") and opened:
+            torch.cuda.current_stream().synchronize()
+            for hb in opened:
+                ops.close_buffer(np.frombuffer(hb, dtype=np.int64))
         return owner
 
     rk = _exchange(keys, send_counts, recv_counts, group)
