@@ -354,10 +354,13 @@ __device__ __forceinline__ vec16 load_l2_keep16(const void* p, unsigned long lon
   return v;
 }
 
-template <class T, class Op, bool INCLUSIVE, int VEC, int IPT>
+// InIt: `const T*` (16-byte aligned: vector loads) or any random-access iterator whose values convert
+// to T (one element per load; a transform_iterator over a pointer, say).
+template <class InIt, class T, class Op, bool INCLUSIVE, int VEC, int IPT>
 __global__ void __launch_bounds__(SCAN_BLOCK, SCANW_CTAS_PER_SM)
-scan_window_kernel(const T* in, T* out, size_t n, size_t tiles, unsigned tiles_per_chunk, T init, bool has_init, const T* init_ptr, Op op,
+scan_window_kernel(InIt in, T* out, size_t n, size_t tiles, unsigned tiles_per_chunk, T init, bool has_init, const T* init_ptr, Op op,
                    tile_state<T> ts, ws_header* hdr) {
+  constexpr bool VECTOR_IN = std::is_same<InIt, const T*>::value;
   if (init_ptr) { init = *init_ptr; has_init = true; }
   constexpr int VPT = IPT / VEC;
   constexpr int NWARPS = SCAN_BLOCK / 32;
@@ -378,15 +381,28 @@ scan_window_kernel(const T* in, T* out, size_t n, size_t tiles, unsigned tiles_p
   auto chunk_first = [&](size_t w, size_t chunk) { return (w * G + chunk) * chunk_wtiles; };
   auto load_tile = [&](vec16 (&r)[VPT], size_t wt, bool keep_in_l2) {
     const size_t base = wt * WT;
-    if (base + WT <= n) {
+    const bool full = base + WT <= n;
+    if constexpr (VECTOR_IN) {
+      if (full) {
+#pragma unroll
+        for (int v = 0; v < VPT; ++v) {
+          const char* p = reinterpret_cast<const char*>(in) + (base + (size_t)(v * 32 + lane) * VEC) * sizeof(T);
+#ifdef TB200_SCANW_EVICT_LAST
+          r[v] = keep_in_l2 ? load_l2_keep16(p, keep) : load_stream16(p);
+#else
+          r[v] = keep_in_l2 ? load_keep16<T>(p) : load_stream16(p);
+#endif
+        }
+        return;
+      }
+    }
+    (void)keep_in_l2;
+    if (full) {
 #pragma unroll
       for (int v = 0; v < VPT; ++v) {
-        const char* p = reinterpret_cast<const char*>(in) + (base + (size_t)(v * 32 + lane) * VEC) * sizeof(T);
-#ifdef TB200_SCANW_EVICT_LAST
-        r[v] = keep_in_l2 ? load_l2_keep16(p, keep) : load_stream16(p);
-#else
-        r[v] = keep_in_l2 ? load_keep16<T>(p) : load_stream16(p);
-#endif
+        T* e = reinterpret_cast<T*>(&r[v]);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) e[k] = (T)in[base + (size_t)(v * 32 + lane) * VEC + k];
       }
     } else {
 #pragma unroll
@@ -395,7 +411,7 @@ scan_window_kernel(const T* in, T* out, size_t n, size_t tiles, unsigned tiles_p
 #pragma unroll
         for (int k = 0; k < VEC; ++k) {
           const size_t i = base + (size_t)(v * 32 + lane) * VEC + k;
-          e[k] = i < n ? in[i] : ID;
+          e[k] = i < n ? (T)in[i] : ID;
         }
       }
     }
@@ -570,6 +586,39 @@ template <class T> size_t scan_workspace_bytes(size_t n) {
   return sizeof(ws_header) + need;   // every route fits
 }
 
+// The windowed route: launches it if the input is large enough for windows to pay (launched = true).
+template <bool INCLUSIVE, class InIt, class T, class Op>
+cudaError_t scan_window_launch(InIt in, T* out, size_t n, T init, bool has_init, const T* d_init, Op op, char* base, ws_header* hdr,
+                               cudaStream_t stream, bool& launched) {
+  launched = false;
+#ifndef TB200_SCAN_NO_WINDOW
+  constexpr int VEC = 16 / sizeof(T);
+  constexpr int IPT2 = scan2_tuning<T>::IPT;
+  const size_t tiles2 = (n + (size_t)SCAN_BLOCK * IPT2 - 1) / ((size_t)SCAN_BLOCK * IPT2);
+  auto kern = scan_window_kernel<InIt, T, Op, INCLUSIVE, VEC, IPT2>;
+  static thread_local int resident[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && resident[dev] == 0) resident[dev] = resident_ctas(kern, SCAN_BLOCK, 0);
+  size_t grid = (dev >= 0 && dev < 64) ? (size_t)resident[dev] : 0;
+  if (grid > SCANW_MAX_GRID) grid = SCANW_MAX_GRID;
+  const unsigned tpc = TB200_SCANW_TPC;
+  if (grid == 0 || tiles2 < 2 * grid * tpc) return cudaSuccess;
+  const size_t windows = (tiles2 + grid * tpc - 1) / (grid * tpc);
+  tile_state<T> tsw;
+  tsw.bind(base + sizeof(ws_header), windows * grid);
+  cudaError_t e3 = cudaMemsetAsync(base, 0, sizeof(ws_header) + tile_state<T>::bytes(windows * grid), stream);
+  if (e3 != cudaSuccess) return e3;
+  launched = true;
+  timed_launch tl(KID_SCAN, stream);
+  kern<<<(unsigned)grid, SCAN_BLOCK, 0, stream>>>(in, out, n, tiles2, tpc, init, has_init, d_init, op, tsw, hdr);
+  log_launch(std::is_pointer<InIt>::value ? "scan_window_kernel" : "scan_window_kernel (generic input)", grid, SCAN_BLOCK, 0, n, stream);
+  return cudaGetLastError();
+#else
+  return cudaSuccess;
+#endif
+}
+
 // Launches the scan on `stream`; no sync.  in == out is allowed.  d_init, if not null, points at an
 // initial value in device memory that replaces (init, has_init); it is read when the kernels run.
 template <bool INCLUSIVE, class InIt, class OutIt, class T, class Op>
@@ -597,25 +646,9 @@ cudaError_t scan_async(InIt in, OutIt out, size_t n, T init, bool has_init, Op o
           constexpr int VEC = 16 / sizeof(T);
 #ifndef TB200_SCAN_NO_WINDOW
           {
-            auto kern = scan_window_kernel<T, Op, INCLUSIVE, VEC, IPT2>;
-            static thread_local int resident[64] = {0};
-            int dev = 0;
-            cudaGetDevice(&dev);
-            if (dev >= 0 && dev < 64 && resident[dev] == 0) resident[dev] = resident_ctas(kern, SCAN_BLOCK, 0);
-            size_t grid = (dev >= 0 && dev < 64) ? (size_t)resident[dev] : 0;
-            if (grid > SCANW_MAX_GRID) grid = SCANW_MAX_GRID;
-            const unsigned tpc = TB200_SCANW_TPC;
-            if (grid > 0 && tiles2 >= 2 * grid * tpc) {
-              const size_t windows = (tiles2 + grid * tpc - 1) / (grid * tpc);
-              tile_state<T> tsw;
-              tsw.bind(base + sizeof(ws_header), windows * grid);
-              cudaError_t e3 = cudaMemsetAsync(base, 0, sizeof(ws_header) + tile_state<T>::bytes(windows * grid), stream);
-              if (e3 != cudaSuccess) return e3;
-              timed_launch tl(KID_SCAN, stream);
-              kern<<<(unsigned)grid, SCAN_BLOCK, 0, stream>>>(in, out, n, tiles2, tpc, init, has_init, d_init, op, tsw, hdr);
-              log_launch("scan_window_kernel", grid, SCAN_BLOCK, 0, n, stream);
-              return cudaGetLastError();
-            }
+            bool launched = false;
+            cudaError_t e3 = scan_window_launch<INCLUSIVE>((const T*)in, out, n, init, has_init, d_init, op, base, hdr, stream, launched);
+            if (launched || e3 != cudaSuccess) return e3;
           }
 #endif
           const size_t tiles_per_chunk = (tiles2 + chunks - 1) / chunks;
@@ -629,6 +662,21 @@ cudaError_t scan_async(InIt in, OutIt out, size_t n, T init, bool has_init, Op o
           log_launch("scan_chunk_reduce_kernel + scan_chunk_kernel", chunks, SCAN_BLOCK, 0, n, stream);
           return cudaGetLastError();
         }
+      }
+    }
+  }
+  // any other input iterator with a contiguous, aligned output of T: the windowed kernel with one
+  // element per load (transform_inclusive_scan / transform_exclusive_scan over a device range)
+  if constexpr (!std::is_pointer<InIt>::value && std::is_pointer<OutIt>::value && is_commutative_op<Op>::value) {
+    using Out = typename std::remove_pointer<OutIt>::type;
+    if constexpr (std::is_same<Out, T>::value && std::is_arithmetic<T>::value && (sizeof(T) == 4 || sizeof(T) == 8)) {
+      size_t chunks = (size_t)current_device_info().sm_count * SCAN2_CTAS_PER_SM;
+      if (chunks > SCAN2_MAX_CHUNKS) chunks = SCAN2_MAX_CHUNKS;
+      const size_t tiles2 = (n + (size_t)SCAN_BLOCK * scan2_tuning<T>::IPT - 1) / ((size_t)SCAN_BLOCK * scan2_tuning<T>::IPT);
+      if (is_aligned16(out) && tiles2 >= SCAN2_MIN_TILES_PER_CHUNK * chunks) {
+        bool launched = false;
+        cudaError_t e3 = scan_window_launch<INCLUSIVE>(in, out, n, init, has_init, d_init, op, base, hdr, stream, launched);
+        if (launched || e3 != cudaSuccess) return e3;
       }
     }
   }

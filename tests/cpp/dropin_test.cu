@@ -23,6 +23,9 @@
 #include <thrust/scan.h>
 #include <thrust/sequence.h>
 #include <thrust/sort.h>
+#include <thrust/transform_reduce.h>
+#include <thrust/transform_scan.h>
+#include <thrust/count.h>
 #include <thrust/tuple.h>
 #include <thrust/unique.h>
 
@@ -58,6 +61,9 @@ struct counting_allocator {
   void deallocate(char* p, size_t) { cudaFree(p); }
 };
 struct by_first { template <class A, class B> __host__ __device__ bool operator()(const A& a, const B& b) const { return thrust::get<0>(a) < thrust::get<0>(b); } };
+
+struct low3 { __host__ __device__ int operator()(int x) const { return x & 7; } };
+struct is_odd_int { __host__ __device__ bool operator()(int x) const { return x & 1; } };
 
 int main() {
   const int n = 1000003;
@@ -225,9 +231,25 @@ int main() {
     got = da2; CHECK(std::equal(hsorted.begin(), hsorted.end(), got.begin()));
     CHECK(thrust::cuda_cub::tb200_overlay::call_count() == before + 4); }
 
+  // callers that arrive through a transform_iterator, on an input large enough for the routes that
+  // large inputs take (the windowed scan with one element per load, the reduce with sixteen loads in flight)
+  { const int big = (1 << 25) + 7;
+    thrust::device_vector<int> bx(big), by(big), bz(big);
+    thrust::sequence(bx.begin(), bx.end(), 5);
+    thrust::transform_inclusive_scan(thrust::device, bx.begin(), bx.end(), by.begin(), low3(), thrust::plus<int>());
+    thrust::transform_exclusive_scan(thrust::device, bx.begin(), bx.end(), bz.begin(), low3(), 11, thrust::plus<int>());
+    thrust::host_vector<int> gy = by, gz = bz;
+    ok = true; { int run = 0; for (int i = 0; i < big && ok; ++i) { ok = gz[i] == 11 + run; run += (i + 5) & 7; ok = ok && gy[i] == run; } }
+    CHECK(ok);
+    const long long odd = thrust::count_if(thrust::device, bx.begin(), bx.end(), is_odd_int());
+    CHECK(odd == (long long)((big + 1) / 2));      // the values run from 5 to big + 4, both odd
+    const long long sq = thrust::transform_reduce(thrust::device, bx.begin(), bx.begin() + 100000, square(), 0LL, thrust::plus<long long>());
+    long long want_sq2 = 0; for (long long i = 0; i < 100000; ++i) want_sq2 += (i + 5) * (i + 5);
+    CHECK(sq == want_sq2); }
+
   // the overlay, not the stock CUB path, served these calls
   std::printf("overlay served %llu calls\n", thrust::cuda_cub::tb200_overlay::call_count());
-  CHECK(thrust::cuda_cub::tb200_overlay::call_count() == 38);
+  CHECK(thrust::cuda_cub::tb200_overlay::call_count() == 42);
   cudaStreamDestroy(s);
   if (cudaDeviceSynchronize() != cudaSuccess) { std::printf("FAILED: sticky CUDA error\n"); ++failures; }
   std::printf(failures ? "dropin_test: %d FAILURES\n" : "dropin_test: all checks passed\n", failures);
