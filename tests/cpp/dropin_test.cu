@@ -17,6 +17,10 @@
 #include <thrust/iterator/transform_iterator.h>
 #include <thrust/iterator/zip_iterator.h>
 #include <thrust/merge.h>
+#include <thrust/mr/allocator.h>
+#include <thrust/mr/disjoint_pool.h>
+#include <thrust/mr/new.h>
+#include <thrust/system/cuda/memory_resource.h>
 #include <thrust/partition.h>
 #include <thrust/reduce.h>
 #include <thrust/extrema.h>
@@ -59,6 +63,13 @@ struct counting_allocator {
   int* served;
   char* allocate(std::ptrdiff_t bytes) { ++*served; char* p = nullptr; if (cudaMalloc(&p, (size_t)bytes) != cudaSuccess) throw std::bad_alloc(); return p; }
   void deallocate(char* p, size_t) { cudaFree(p); }
+};
+// a device memory resource that counts what reaches it: the upstream of a thrust::mr pool
+struct counting_resource final : thrust::mr::memory_resource<thrust::cuda::memory_resource::pointer> {
+  thrust::cuda::memory_resource upstream;
+  int allocations = 0;
+  pointer do_allocate(std::size_t bytes, std::size_t alignment) override { ++allocations; return upstream.do_allocate(bytes, alignment); }
+  void do_deallocate(pointer p, std::size_t bytes, std::size_t alignment) override { upstream.do_deallocate(p, bytes, alignment); }
 };
 struct by_first { template <class A, class B> __host__ __device__ bool operator()(const A& a, const B& b) const { return thrust::get<0>(a) < thrust::get<0>(b); } };
 
@@ -231,6 +242,26 @@ int main() {
     got = da2; CHECK(std::equal(hsorted.begin(), hsorted.end(), got.begin()));
     CHECK(thrust::cuda_cub::tb200_overlay::call_count() == before + 4); }
 
+  // thrust::mr: a pool resource behind thrust::mr::allocator handed to par(alloc) -- the temporary
+  // storage of the kernels comes out of the pool, and the second call is served from what the first
+  // one returned to it (nothing new reaches the upstream resource)
+  { counting_resource upstream;
+    thrust::mr::new_delete_resource bookkeeper;
+    typedef thrust::mr::disjoint_unsynchronized_pool_resource<counting_resource, thrust::mr::new_delete_resource> pool_t;
+    pool_t pool(&upstream, &bookkeeper);
+    thrust::mr::allocator<char, pool_t> alloc(&pool);
+    const unsigned long long before = thrust::cuda_cub::tb200_overlay::call_count();
+    thrust::device_vector<int> ds(d.begin(), d.end());
+    thrust::sort(thrust::cuda::par(alloc), ds.begin(), ds.end());
+    const int after_first = upstream.allocations;
+    thrust::device_vector<int> ds2(d.begin(), d.end());
+    thrust::sort(thrust::cuda::par(alloc), ds2.begin(), ds2.end());
+    std::vector<int> hsorted(h.begin(), h.end()); std::sort(hsorted.begin(), hsorted.end());
+    got = ds; CHECK(std::equal(hsorted.begin(), hsorted.end(), got.begin()));
+    got = ds2; CHECK(std::equal(hsorted.begin(), hsorted.end(), got.begin()));
+    CHECK(after_first >= 1 && upstream.allocations == after_first);
+    CHECK(thrust::cuda_cub::tb200_overlay::call_count() == before + 2); }
+
   // callers that arrive through a transform_iterator, on an input large enough for the routes that
   // large inputs take (the windowed scan with one element per load, the reduce with sixteen loads in flight)
   { const int big = (1 << 25) + 7;
@@ -249,7 +280,7 @@ int main() {
 
   // the overlay, not the stock CUB path, served these calls
   std::printf("overlay served %llu calls\n", thrust::cuda_cub::tb200_overlay::call_count());
-  CHECK(thrust::cuda_cub::tb200_overlay::call_count() == 42);
+  CHECK(thrust::cuda_cub::tb200_overlay::call_count() == 44);
   cudaStreamDestroy(s);
   if (cudaDeviceSynchronize() != cudaSuccess) { std::printf("FAILED: sticky CUDA error\n"); ++failures; }
   std::printf(failures ? "dropin_test: %d FAILURES\n" : "dropin_test: all checks passed\n", failures);

@@ -24,4 +24,4 @@ def test_thrust_program_runs_on_overlay(tb, tmp_path):
     assert r.returncode == 0, r.stdout + r.stderr
     r = subprocess.run([exe], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0 and "all checks passed" in r.stdout, r.stdout + r.stderr
-    assert "overlay served 42 calls" in r.stdout
+    assert "overlay served 44 calls" in r.stdout
