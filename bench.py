@@ -286,6 +286,12 @@ def bench_others(torch, tb, lib, peak):
     record("merge_by_key 2 x 2^27 (u64, u32)", 2 * na, 24,
            lambda: lib.tb200_merge_by_key(p(ka), p(va), na, p(kb), p(vb), na, p(ko), p(vo), 7, 4, 0, p(ws), C.byref(need), st),
            cpu=cpu_time(lambda: ora.merge_by_key(hma, hmb, hmva, hmvb), cpu_n))
+    # the set operations on the same two sorted ranges (keys only): 8 B in and at most 8 B out per input item
+    cnt = torch.zeros(1, dtype=torch.int64, device="cuda")
+    ws, need = ws_for("tb200_set_operation", 0, None, na, None, na, None, None, None, None, 7, 0, 0, None)
+    for code, nm in ((0, "set_union"), (1, "set_intersection")):
+        record("%s 2 x 2^27 u64" % nm, 2 * na, 16 if code == 0 else 8,
+               lambda c=code: lib.tb200_set_operation(c, p(ka), na, p(kb), na, None, None, p(ko), None, 7, 0, 0, p(cnt), p(ws), C.byref(need), st))
     del ka, kb, va, vb, ko, vo
     n64 = 1 << 27
     k0 = dev(dg.sort_keys_u64_40bit(n64))

@@ -12,13 +12,15 @@
 // merged positions along its merge path (any cut works: nothing is decided from tile-local
 // information alone), and three stream-ordered steps with no host round trip do the rest:
 //   1. set_partition_kernel  one thread per tile boundary: a binary search along the diagonal;
-//   2. set_tile_kernel<COUNT> every element finds its merged position (a binary search inside the
-//                            tile's slice of the other side), its rank r (a galloping search
-//                            backwards, one probe when keys are unique) and probes the other side's
-//                            element number r; the tile's number of kept elements goes to an array
-//                            that scan.cuh scans;
-//   3. set_tile_kernel<EMIT>  the same, then a block scan over the kept flags in merged order and
-//                            the kept elements (and their values) are written out in order.
+//   2. set_tile_kernel<COUNT> every thread takes eight consecutive positions of the tile's merge: one
+//                            binary search along its diagonal finds where they start in A and in B,
+//                            one galloping search backwards per side gives the ranks of the two
+//                            current elements inside their runs; then it merges serially, keeping
+//                            the ranks up to date with one comparison per step, and decides each
+//                            element with one probe of the other side's element number r; the
+//                            tile's number of kept elements goes to an array that scan.cuh scans;
+//   3. set_tile_kernel<EMIT>  the same, then a block scan over the threads' kept counts and every
+//                            thread writes its kept elements (and their values) in order.
 // The workspace is 24 bytes per tile; sizes are 64-bit throughout.
 #pragma once
 #include "common.cuh"
@@ -27,8 +29,8 @@
 namespace tb200 {
 
 enum set_op : int { SET_UNION = 0, SET_INTERSECTION = 1, SET_DIFFERENCE = 2, SET_SYMMETRIC_DIFFERENCE = 3 };
-constexpr int SETOP_BLOCK = 512;
-constexpr int SETOP_IPT = 4;
+constexpr int SETOP_BLOCK = 256;
+constexpr int SETOP_IPT = 8;
 constexpr int SETOP_TILE = SETOP_BLOCK * SETOP_IPT;
 
 // first index in [0, n) whose element does not order before x
@@ -77,51 +79,55 @@ __global__ void __launch_bounds__(SETOP_BLOCK)
 set_tile_kernel(ItA a, size_t na, ItB b, size_t nb, VItA va, VItB vb, KeyOutIt out, ValOutIt vout, int op, Comp comp, const unsigned long long* split,
                 unsigned long long* totals, const unsigned long long* bases, size_t tiles, ws_header* hdr, const ws_header* scan_hdr,
                 unsigned long long* d_count) {
-  __shared__ unsigned s_src[EMIT ? SETOP_TILE : 1];            // by merged position: item number | kept << 31
   __shared__ unsigned s_warp[SETOP_BLOCK / 32];
   const size_t tile = blockIdx.x;
   const size_t d0 = tile * SETOP_TILE;
   const size_t a0 = split[tile], a1 = split[tile + 1];
   const size_t d1 = d0 + SETOP_TILE < na + nb ? d0 + SETOP_TILE : na + nb;
   const size_t b0 = d0 - a0, b1 = d1 - a1;
-  const unsigned ca = (unsigned)(a1 - a0), count = (unsigned)(d1 - d0);
-  if constexpr (EMIT) {
-    if (count < SETOP_TILE) {
-      for (unsigned p = threadIdx.x; p < SETOP_TILE; p += SETOP_BLOCK) s_src[p] = 0;
-      __syncthreads();
-    }
+  const unsigned count = (unsigned)(d1 - d0);
+  // this thread's SETOP_IPT consecutive positions of the merge: where they start in A and in B
+  unsigned t0 = threadIdx.x * SETOP_IPT; if (t0 > count) t0 = count;
+  unsigned t1 = t0 + SETOP_IPT; if (t1 > count) t1 = count;
+  size_t ai = a0 + set_merge_split(a + a0, a1 - a0, b + b0, b1 - b0, (size_t)t0, comp);
+  size_t bi = b0 + (t0 - (ai - a0));
+  // ranks of the two current elements inside their runs of equivalent elements
+  size_t ra = 0, rb = 0;
+  T ka = T(), kb = T();
+  if (t0 < t1) {
+    if (ai < na) { ka = a[ai]; ra = set_run_rank(a, ai, ka, comp); }
+    if (bi < nb) { kb = b[bi]; rb = set_run_rank(b, bi, kb, comp); }
   }
-  unsigned kept = 0;
+  unsigned keep_bits = 0, from_b = 0, kept = 0;
+  unsigned src[SETOP_IPT];                                      // offset of every position's element inside its slice
 #pragma unroll
-  for (int it = 0; it < SETOP_IPT; ++it) {
-    const unsigned k = threadIdx.x + it * SETOP_BLOCK;
-    if (k >= count) break;
+  for (int i = 0; i < SETOP_IPT; ++i) {
+    src[i] = 0;
+    if (t0 + i >= t1) continue;
+    const bool take_a = ai < a1 && (bi >= b1 || !comp(kb, ka));   // A first among equivalent elements
     bool keep;
-    unsigned pos;
-    if (k < ca) {
-      const size_t i = a0 + k;
-      const T x = a[i];
-      const size_t lb = b0 + set_lower_bound(b + b0, b1 - b0, x, comp);        // B's elements that order before x
-      pos = k + (unsigned)(lb - b0);
+    if (take_a) {
+      // B's elements ahead of this one in the merge are exactly those that order before it: bi of them
       if (op == SET_UNION) keep = true;
       else {
-        const size_t r = set_run_rank(a, i, x, comp);
-        const bool other_has = lb + r < nb && !comp(x, b[lb + r]);            // B holds more than r elements equivalent to x
+        const bool other_has = bi + ra < nb && !comp(ka, b[bi + ra]);         // B holds more than ra elements equivalent to it
         keep = op == SET_INTERSECTION ? other_has : !other_has;
       }
+      src[i] = (unsigned)(ai - a0);
+      ++ai;
+      if (ai < na) { const T next = a[ai]; ra = comp(ka, next) ? 0 : ra + 1; ka = next; }
     } else {
-      const size_t j = b0 + (k - ca);
-      const T y = b[j];
-      const size_t ub = a0 + set_upper_bound(a + a0, a1 - a0, y, comp);        // A's elements that order before y or are equivalent
-      pos = (k - ca) + (unsigned)(ub - a0);
+      // A's elements ahead of this one are those that order before it or are equivalent: ai of them
       if (op == SET_UNION || op == SET_SYMMETRIC_DIFFERENCE) {
-        const size_t r = set_run_rank(b, j, y, comp);
-        const bool other_has = ub > r && !comp(a[ub - 1 - r], y);             // A holds more than r elements equivalent to y
+        const bool other_has = ai > rb && !comp(a[ai - 1 - rb], kb);          // A holds more than rb elements equivalent to it
         keep = !other_has;
       } else keep = false;
+      src[i] = (unsigned)(bi - b0);
+      from_b |= 1u << i;
+      ++bi;
+      if (bi < nb) { const T next = b[bi]; rb = comp(kb, next) ? 0 : rb + 1; kb = next; }
     }
-    kept += keep ? 1u : 0u;
-    if constexpr (EMIT) s_src[pos] = k | (keep ? 0x80000000u : 0u);
+    if (keep) { keep_bits |= 1u << i; ++kept; }
   }
   const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if constexpr (!EMIT) {
@@ -134,28 +140,22 @@ set_tile_kernel(ItA a, size_t na, ItB b, size_t nb, VItA va, VItB vb, KeyOutIt o
       totals[tile] = total;
     }
   } else {
-    __syncthreads();
-    unsigned mine[SETOP_IPT];
-    unsigned c = 0;
-#pragma unroll
-    for (int q = 0; q < SETOP_IPT; ++q) { mine[q] = s_src[threadIdx.x * SETOP_IPT + q]; c += mine[q] >> 31; }
-    const unsigned incl = warp_inclusive_scan(c, plus_op());
+    const unsigned incl = warp_inclusive_scan(kept, plus_op());
     if (lane == 31) s_warp[warp] = incl;
     __syncthreads();
     unsigned before = 0;
     for (unsigned w = 0; w < warp; ++w) before += s_warp[w];
     const unsigned long long base = bases[tile];
-    size_t at = (size_t)base + before + (incl - c);
+    size_t at = (size_t)base + before + (incl - kept);
 #pragma unroll
-    for (int q = 0; q < SETOP_IPT; ++q) {
-      if (mine[q] >> 31) {
-        const unsigned k = mine[q] & 0x7fffffffu;
-        if (k < ca) {
-          out[at] = a[a0 + k];
-          if constexpr (HAS_V) vout[at] = va[a0 + k];
+    for (int i = 0; i < SETOP_IPT; ++i) {
+      if ((keep_bits >> i) & 1) {
+        if ((from_b >> i) & 1) {
+          out[at] = b[b0 + src[i]];
+          if constexpr (HAS_V) vout[at] = vb[b0 + src[i]];
         } else {
-          out[at] = b[b0 + (k - ca)];
-          if constexpr (HAS_V) vout[at] = vb[b0 + (k - ca)];
+          out[at] = a[a0 + src[i]];
+          if constexpr (HAS_V) vout[at] = va[a0 + src[i]];
         }
         ++at;
       }
