@@ -453,6 +453,9 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    # one process per GPU: keep each rank's pinned buffers and copies on its GPU's socket (N = 1 keeps
+    # every host thread for the CPU baseline leg)
+    numa_node = sharded.bind_to_gpu_numa_node(local_rank) if world > 1 else None
     lo, hi = rank * N_KEYS // world, (rank + 1) * N_KEYS // world
     n_local = hi - lo
     h_keys = torch.from_numpy(dg.sort_keys_u32(n_local, start=lo)).pin_memory()
@@ -599,6 +602,7 @@ def run_ours(args):
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u32", "data": "synthetic",
         "config": {"workload": WORKLOAD, "n": N_KEYS, "per_gpu": n_local,
                    "l2": "2 GiB of input per step (> 126 MB L2); the pristine input is restored by a 2 GiB device copy between timed steps",
+                   "host_numa_node_of_rank0": numa_node,
                    "parallelism": "1 GPU" if world == 1 else "%d GPUs: splitters from an all-gathered 12-bit digit histogram, one scatter kernel per GPU storing each pair into the owning GPU's receive buffer over NVLink (CUDA IPC), local radix sort of what arrived" % world},
         "roofline": roofline, "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
         "wall_s_timed_region": t_wall, "verified": verified, "stages_ms": stages,

@@ -41,6 +41,35 @@ def _plumbing_view(t):
     return t.view(_SIGNED_VIEW[t.dtype]) if t.dtype in _SIGNED_VIEW else t
 
 
+def bind_to_gpu_numa_node(device_index):
+    """Host-side placement for one-process-per-GPU jobs: restricts this process to the CPUs of the
+    NUMA node that the GPU's PCIe link hangs off, so that the pinned buffers it allocates afterwards
+    (first touch) and its copies stay on that socket instead of crossing the inter-socket link.
+    Reads sysfs only; returns the node, or None when the topology is not visible, the node has no
+    CPU this process may use, or there is a single node (nothing is changed then)."""
+    import os
+    try:
+        props = torch.cuda.get_device_properties(device_index)
+        dev = "%04x:%02x:%02x.0" % (props.pci_domain_id, props.pci_bus_id, props.pci_device_id)
+        with open("/sys/bus/pci/devices/%s/numa_node" % dev) as f:
+            node = int(f.read().strip())
+        nodes = [d for d in os.listdir("/sys/devices/system/node") if d.startswith("node") and d[4:].isdigit()]
+        if node < 0 or len(nodes) < 2:
+            return None
+        with open("/sys/devices/system/node/node%d/cpulist" % node) as f:
+            cpus = set()
+            for part in f.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        usable = cpus & os.sched_getaffinity(0)
+        if not usable:
+            return None
+        os.sched_setaffinity(0, usable)
+        return node
+    except (OSError, ValueError, AttributeError, RuntimeError, AssertionError):
+        return None
+
+
 class DeviceOps:
     """The product path: every compute step is a C-ABI call on CUDA tensors."""
 
