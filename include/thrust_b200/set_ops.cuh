@@ -10,21 +10,21 @@
 // dropped depends only on its rank r inside its own run of equivalent elements and on whether the
 // other side has more than r such elements.  So the merge is cut into tiles of 2048 consecutive
 // merged positions along its merge path (any cut works: nothing is decided from tile-local
-// information alone), and three stream-ordered steps with no host round trip do the rest:
+// information alone), and two stream-ordered launches with no host round trip do the rest:
 //   1. set_partition_kernel  one thread per tile boundary: a binary search along the diagonal;
-//   2. set_tile_kernel<COUNT> every thread takes eight consecutive positions of the tile's merge: one
+//   2. set_tile_kernel       every thread takes eight consecutive positions of the tile's merge: one
 //                            binary search along its diagonal finds where they start in A and in B,
 //                            one galloping search backwards per side gives the ranks of the two
 //                            current elements inside their runs; then it merges serially, keeping
 //                            the ranks up to date with one comparison per step, and decides each
-//                            element with one probe of the other side's element number r; the
-//                            tile's number of kept elements goes to an array that scan.cuh scans;
-//   3. set_tile_kernel<EMIT>  the same, then a block scan over the threads' kept counts and every
-//                            thread writes its kept elements (and their values) in order.
+//                            element with one probe of the other side's element number r.  The
+//                            tile's number of kept elements is published, a decoupled look-back
+//                            over the earlier tiles' counts (tiles by atomic ticket, bounded waits)
+//                            gives the tile's place in the output, and every thread writes its
+//                            kept elements (and their values) in order: one pass over the inputs.
 // The workspace is 24 bytes per tile; sizes are 64-bit throughout.
 #pragma once
 #include "common.cuh"
-#include "scan.cuh"
 
 namespace tb200 {
 
@@ -74,13 +74,17 @@ __global__ void __launch_bounds__(256) set_partition_kernel(ItA a, size_t na, It
   split[t] = set_merge_split(a, na, b, nb, d, comp);
 }
 
-template <bool EMIT, bool HAS_V, class T, class ItA, class ItB, class VItA, class VItB, class KeyOutIt, class ValOutIt, class Comp>
+template <bool HAS_V, class T, class ItA, class ItB, class VItA, class VItB, class KeyOutIt, class ValOutIt, class Comp>
 __global__ void __launch_bounds__(SETOP_BLOCK)
 set_tile_kernel(ItA a, size_t na, ItB b, size_t nb, VItA va, VItB vb, KeyOutIt out, ValOutIt vout, int op, Comp comp, const unsigned long long* split,
-                unsigned long long* totals, const unsigned long long* bases, size_t tiles, ws_header* hdr, const ws_header* scan_hdr,
-                unsigned long long* d_count) {
+                tile_state<unsigned long long> ts, size_t tiles, ws_header* hdr, unsigned long long* d_count) {
   __shared__ unsigned s_warp[SETOP_BLOCK / 32];
-  const size_t tile = blockIdx.x;
+  __shared__ unsigned s_ticket;
+  __shared__ unsigned long long s_base;
+  // tiles are taken in the order in which CTAs start, so a tile only ever waits for tiles whose CTAs run
+  if (threadIdx.x == 0) s_ticket = atomicAdd(&hdr->ticket, 1u);
+  __syncthreads();
+  const size_t tile = s_ticket;
   const size_t d0 = tile * SETOP_TILE;
   const size_t a0 = split[tile], a1 = split[tile + 1];
   const size_t d1 = d0 + SETOP_TILE < na + nb ? d0 + SETOP_TILE : na + nb;
@@ -129,51 +133,53 @@ set_tile_kernel(ItA a, size_t na, ItB b, size_t nb, VItA va, VItB vb, KeyOutIt o
     }
     if (keep) { keep_bits |= 1u << i; ++kept; }
   }
+  // where the tile's output starts: its count is published, the counts of the tiles before it are
+  // folded by a decoupled look-back (bounded waits), the running total is published for the tiles behind
   const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if constexpr (!EMIT) {
-    kept = __reduce_add_sync(0xffffffffu, kept);
-    if (lane == 0) s_warp[warp] = kept;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      unsigned total = 0;
-      for (int w = 0; w < SETOP_BLOCK / 32; ++w) total += s_warp[w];
-      totals[tile] = total;
+  const unsigned incl = warp_inclusive_scan(kept, plus_op());
+  if (lane == 31) s_warp[warp] = incl;
+  __syncthreads();
+  unsigned before = 0, tile_total = 0;
+  for (unsigned w = 0; w < SETOP_BLOCK / 32; ++w) { if (w < warp) before += s_warp[w]; tile_total += s_warp[w]; }
+  if (warp == 0) {
+    unsigned long long prefix = 0;
+    if (tile == 0) {
+      if (lane == 0) ts.publish(0, TILE_INCLUSIVE, (unsigned long long)tile_total);
+    } else {
+      if (lane == 0) ts.publish(tile, TILE_AGGREGATE, (unsigned long long)tile_total);
+      prefix = lookback_prefix<unsigned long long>(ts, tile, plus_op(), &hdr->error);
+      if (lane == 0) ts.publish(tile, TILE_INCLUSIVE, prefix + tile_total);
     }
-  } else {
-    const unsigned incl = warp_inclusive_scan(kept, plus_op());
-    if (lane == 31) s_warp[warp] = incl;
-    __syncthreads();
-    unsigned before = 0;
-    for (unsigned w = 0; w < warp; ++w) before += s_warp[w];
-    const unsigned long long base = bases[tile];
-    size_t at = (size_t)base + before + (incl - kept);
+    if (lane == 0) s_base = prefix;
+  }
+  __syncthreads();
+  const unsigned long long base = s_base;
+  size_t at = (size_t)base + before + (incl - kept);
 #pragma unroll
-    for (int i = 0; i < SETOP_IPT; ++i) {
-      if ((keep_bits >> i) & 1) {
-        if ((from_b >> i) & 1) {
-          out[at] = b[b0 + src[i]];
-          if constexpr (HAS_V) vout[at] = vb[b0 + src[i]];
-        } else {
-          out[at] = a[a0 + src[i]];
-          if constexpr (HAS_V) vout[at] = va[a0 + src[i]];
-        }
-        ++at;
+  for (int i = 0; i < SETOP_IPT; ++i) {
+    if ((keep_bits >> i) & 1) {
+      if ((from_b >> i) & 1) {
+        out[at] = b[b0 + src[i]];
+        if constexpr (HAS_V) vout[at] = vb[b0 + src[i]];
+      } else {
+        out[at] = a[a0 + src[i]];
+        if constexpr (HAS_V) vout[at] = va[a0 + src[i]];
       }
+      ++at;
     }
-    if (tile + 1 == tiles && threadIdx.x == SETOP_BLOCK - 1) {
-      const unsigned long long total = base + before + incl;
-      hdr->count = total;
-      hdr->error = scan_hdr->error;
-      if (d_count) *d_count = total;
-    }
+  }
+  if (tile + 1 == tiles && threadIdx.x == 0) {
+    const unsigned long long total = base + tile_total;
+    hdr->count = total;
+    if (d_count) *d_count = total;
   }
 }
 
 inline size_t set_op_tiles(size_t na, size_t nb) { return (na + nb + SETOP_TILE - 1) / SETOP_TILE; }
-// header | split [tiles + 1] | totals [tiles] | bases [tiles] | the scan's workspace
+// header | split [tiles + 1] | one look-back descriptor per tile
 inline size_t set_op_workspace_bytes(size_t na, size_t nb) {
   const size_t tiles = set_op_tiles(na, nb);
-  return sizeof(ws_header) + align_up((tiles + 1) * 8, 256) + 2 * align_up(tiles * 8 + 8, 256) + scan_workspace_bytes<unsigned long long>(tiles + 1);
+  return sizeof(ws_header) + align_up((tiles + 1) * 8, 256) + tile_state<unsigned long long>::bytes(tiles + 1);
 }
 
 // A[0, na) and B[0, nb) sorted by comp; keys (and, HAS_V, the values that travel with the kept keys:
@@ -188,21 +194,22 @@ cudaError_t set_operation_async(int op, ItA a, size_t na, ItB b, size_t nb, VItA
   if (op < SET_UNION || op > SET_SYMMETRIC_DIFFERENCE || tiles >= 0x7fffffffull) return cudaErrorInvalidValue;
   char* base = static_cast<char*>(ws);
   ws_header* hdr = reinterpret_cast<ws_header*>(base);
-  char* p = base + sizeof(ws_header);
-  unsigned long long* split = reinterpret_cast<unsigned long long*>(p); p += align_up((tiles + 1) * 8, 256);
-  unsigned long long* totals = reinterpret_cast<unsigned long long*>(p); p += align_up(tiles * 8 + 8, 256);
-  unsigned long long* bases = reinterpret_cast<unsigned long long*>(p); p += align_up(tiles * 8 + 8, 256);
-  void* scan_ws = p;
+  unsigned long long* split = reinterpret_cast<unsigned long long*>(base + sizeof(ws_header));
+  char* desc = base + sizeof(ws_header) + align_up((tiles + 1) * 8, 256);
+  if (tiles == 0) {
+    cudaError_t e0 = cudaMemsetAsync(hdr, 0, sizeof(ws_header), stream);
+    if (e0 != cudaSuccess) return e0;
+    return d_count ? cudaMemsetAsync(d_count, 0, sizeof(unsigned long long), stream) : cudaSuccess;
+  }
+  // header (ticket, status, count) and descriptors start out zero; the split array is written in full
   cudaError_t e = cudaMemsetAsync(hdr, 0, sizeof(ws_header), stream);
   if (e != cudaSuccess) return e;
-  if (tiles == 0) return d_count ? cudaMemsetAsync(d_count, 0, sizeof(unsigned long long), stream) : cudaSuccess;
+  if ((e = cudaMemsetAsync(desc, 0, tile_state<unsigned long long>::bytes(tiles + 1), stream)) != cudaSuccess) return e;
+  tile_state<unsigned long long> ts;
+  ts.bind(desc, tiles + 1);
   set_partition_kernel<<<(unsigned)((tiles + 1 + 255) / 256), 256, 0, stream>>>(a, na, b, nb, tiles, comp, split);
-  set_tile_kernel<false, HAS_V, T><<<(unsigned)tiles, SETOP_BLOCK, 0, stream>>>(a, na, b, nb, va, vb, out, vout, op, comp, split, totals, bases, tiles, hdr,
-                                                                                 static_cast<const ws_header*>(scan_ws), d_count);
-  if ((e = scan_async<false>((const unsigned long long*)totals, bases, tiles, 0ull, true, plus_op(), scan_ws, stream)) != cudaSuccess) return e;
-  set_tile_kernel<true, HAS_V, T><<<(unsigned)tiles, SETOP_BLOCK, 0, stream>>>(a, na, b, nb, va, vb, out, vout, op, comp, split, totals, bases, tiles, hdr,
-                                                                                static_cast<const ws_header*>(scan_ws), d_count);
-  log_launch("set_partition_kernel + set_tile_kernel x2 + scan", tiles, SETOP_BLOCK, 0, na + nb, stream);
+  set_tile_kernel<HAS_V, T><<<(unsigned)tiles, SETOP_BLOCK, 0, stream>>>(a, na, b, nb, va, vb, out, vout, op, comp, split, ts, tiles, hdr, d_count);
+  log_launch("set_partition_kernel + set_tile_kernel", tiles, SETOP_BLOCK, 0, na + nb, stream);
   return cudaGetLastError();
 }
 
