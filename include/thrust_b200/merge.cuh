@@ -20,13 +20,36 @@
 namespace tb200 {
 
 constexpr int MERGE_BLOCK = 256;
+// Tunables: items per thread and resident CTAs per SM asked of the compiler (a register cap) for
+// items of up to 8 and up to 12 bytes (key + payload).  The merge kernels are bound by the latency
+// of their barrier-separated phases, not by issue slots or memory, so small tiles and many resident
+// CTAs pay: measured on B200, 11 items per thread at 8 CTAs per SM (32 registers) for 8-byte items
+// and 7 items at 7 CTAs (36 registers) for 12-byte items took a merge pass over 2^26 (u32, f32)
+// pairs from 0.545 to 0.32 ms and merge_by_key of 2 x 2^27 (u64, u32) from 2.16 to 1.79 ms against
+// 15 / 11 items at the compiler's own 58 registers (4 CTAs).  The block sort gains little (5 CTAs).
+#ifndef TB200_MERGE_IPT8
+#define TB200_MERGE_IPT8 11
+#endif
+#ifndef TB200_MERGE_IPT12
+#define TB200_MERGE_IPT12 7
+#endif
+#ifndef TB200_MERGE_CTAS8
+#define TB200_MERGE_CTAS8 8
+#endif
+#ifndef TB200_MERGE_CTAS12
+#define TB200_MERGE_CTAS12 7
+#endif
+#ifndef TB200_BSORT_CTAS8
+#define TB200_BSORT_CTAS8 5
+#endif
 
 // Items per thread: tuned for the small types, then whatever keeps the staged tile (keys and
 // payloads of 256 * IPT items) inside 44 KB of static shared memory, as the reference sizes its
 // tiles by sizeof(T) (thrust/system/cuda/detail/merge.h:301-360).
 constexpr int MERGE_SMEM_BUDGET = 44 * 1024;
 template <int KB, int VB> struct merge_tuning {
-  static constexpr int TUNED = (KB + VB) <= 8 ? 15 : ((KB + VB) <= 12 ? 11 : 9);
+  static constexpr int TUNED = (KB + VB) <= 8 ? TB200_MERGE_IPT8 : ((KB + VB) <= 12 ? TB200_MERGE_IPT12 : 9);
+  static constexpr int MIN_CTAS = (KB + VB) <= 8 ? TB200_MERGE_CTAS8 : ((KB + VB) <= 12 ? TB200_MERGE_CTAS12 : 1);
   static constexpr int FIT = MERGE_SMEM_BUDGET / (MERGE_BLOCK * (KB + VB));
   static constexpr int IPT = TUNED < FIT ? TUNED : (FIT < 1 ? 1 : FIT);
   static_assert(MERGE_BLOCK * IPT * (KB + VB) + KB <= 48 * 1024, "key + payload too large for the merge tile (more than 160 bytes per item)");
@@ -96,7 +119,7 @@ merge_partition_kernel(KeyItA ka, KeyItB kb, merge_geometry g, size_t num_tiles,
 }
 
 template <class KeyItA, class KeyItB, class ValItA, class ValItB, class KeyOutIt, class ValOutIt, class K, class V, bool HAS_V, class Comp, int IPT>
-__global__ void __launch_bounds__(MERGE_BLOCK)
+__global__ void __launch_bounds__(MERGE_BLOCK, merge_tuning<sizeof(K), HAS_V ? sizeof(V) : 0>::MIN_CTAS)
 merge_kernel(KeyItA ka, KeyItB kb, ValItA va, ValItB vb, KeyOutIt ko, ValOutIt vo, merge_geometry g, Comp comp, const size_t* a_split) {
   constexpr int TILE = MERGE_BLOCK * IPT;
   TB200_SHARED_ARRAY(K, s_key, TILE + 1);
@@ -209,7 +232,7 @@ template <int KB, int VB> struct block_sort_tuning {
 };
 
 template <class KeyIt, class ValIt, class KeyOutIt, class ValOutIt, class K, class V, bool HAS_V, class Comp, int IPT>
-__global__ void __launch_bounds__(MERGE_BLOCK)
+__global__ void __launch_bounds__(MERGE_BLOCK, sizeof(K) <= 4 ? TB200_BSORT_CTAS8 : 1)
 block_sort_kernel(KeyIt keys, ValIt vals, KeyOutIt keys_out, ValOutIt vals_out, size_t n, Comp comp) {
   constexpr int TILE = MERGE_BLOCK * IPT;
   TB200_SHARED_ARRAY(K, s_key, TILE + 1);
