@@ -27,7 +27,10 @@ constexpr int RBK_STREAM_BLOCK = 256;
 // Measured on B200, 2^28 int32 keys + fp32 values, runs of mean length 4: 1.24 ms with two rows per batch
 // and four CTAs per SM (three or four rows: 1.27, registers spill; five CTAs: 1.48) against 1.37 ms
 // for the single-pass kernel.
-constexpr int RBK_STREAM_CTAS_PER_SM = 4;
+#ifndef TB200_RBK_STREAM_CTAS
+#define TB200_RBK_STREAM_CTAS 4
+#endif
+constexpr int RBK_STREAM_CTAS_PER_SM = TB200_RBK_STREAM_CTAS;
 constexpr int RBK_STREAM_ROWS = 2;
 constexpr size_t RBK_STREAM_MIN_ITEMS = (size_t)1 << 24;
 
