@@ -39,6 +39,9 @@ constexpr int MERGE_BLOCK = 256;
 #ifndef TB200_MERGE_CTAS12
 #define TB200_MERGE_CTAS12 7
 #endif
+#ifndef TB200_BSORT_IPT8
+#define TB200_BSORT_IPT8 16
+#endif
 #ifndef TB200_BSORT_CTAS8
 #define TB200_BSORT_CTAS8 5
 #endif
@@ -227,7 +230,7 @@ cudaError_t merge_async(KeyItA ka, size_t na, KeyItB kb, size_t nb, ValItA va, V
 template <int KB, int VB> struct block_sort_tuning {
   // power-of-two friendly tile of 256 * IPT items whose keys (+ a 2-byte index each) fit 44 KB of shared memory
   static constexpr int FIT = MERGE_SMEM_BUDGET / (MERGE_BLOCK * (KB + 2));
-  static constexpr int IPT = (KB + VB) <= 8 ? 16 : (FIT >= 8 ? 8 : FIT >= 4 ? 4 : FIT >= 2 ? 2 : 1);
+  static constexpr int IPT = (KB + VB) <= 8 ? TB200_BSORT_IPT8 : (FIT >= 8 ? 8 : FIT >= 4 ? 4 : FIT >= 2 ? 2 : 1);
   static_assert(MERGE_BLOCK * IPT * (KB + 2) + KB + 2 <= 48 * 1024, "key too large for the block sort tile (more than 170 bytes)");
 };
 
