@@ -134,7 +134,10 @@ scan_kernel(InIt in, OutIt out, size_t n, T init, bool has_init, const T* init_p
 // 0.530; three CTAs: 0.519; five to eight CTAs: 0.53-0.57) against 0.63 ms for the single-pass kernel;
 // the first pass runs at 99 % and the second at 94 % of the measured copy bandwidth.
 constexpr int SCAN2_CTAS_PER_SM = 4;
-template <class T> struct scan2_tuning { static constexpr int IPT = (int)(64 / sizeof(T)); };
+#ifndef TB200_SCAN2_TILE_BYTES_PER_THREAD
+#define TB200_SCAN2_TILE_BYTES_PER_THREAD 64
+#endif
+template <class T> struct scan2_tuning { static constexpr int IPT = (int)(TB200_SCAN2_TILE_BYTES_PER_THREAD / sizeof(T)); };
 constexpr int SCAN2_MAX_CHUNKS = 2048;
 constexpr size_t SCAN2_MIN_TILES_PER_CHUNK = 2;   // shorter chunks (n below ~5 M four-byte items) take the single-pass kernel
 
