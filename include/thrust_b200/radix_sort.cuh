@@ -161,9 +161,12 @@ radix_scan_hist_kernel(radix_ctrl* ctrl, size_t n, int first_pass) {
 #ifndef TB200_SWEEP_MATCH_EVERY
 #define TB200_SWEEP_MATCH_EVERY 0
 #endif
+#ifndef TB200_SWEEP_IPT_84
+#define TB200_SWEEP_IPT_84 12
+#endif
 template <int KB, int VB> struct onesweep_tuning {
   // items per thread; two 512-thread CTAs per SM (64 registers per thread, ~80 KB of staging each)
-  static constexpr int IPT = KB <= 4 ? (VB == 0 ? 18 : VB <= 4 ? TB200_SWEEP_IPT_44 : 12) : (VB == 0 ? 12 : VB <= 4 ? 10 : 8);
+  static constexpr int IPT = KB <= 4 ? (VB == 0 ? 18 : VB <= 4 ? TB200_SWEEP_IPT_44 : 12) : (VB == 0 ? 12 : VB <= 4 ? TB200_SWEEP_IPT_84 : 8);
 };
 
 // What distinguishes a radix digit pass from the multi-GPU bucket scatter: how a key maps to one of
