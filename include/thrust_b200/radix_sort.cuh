@@ -6,14 +6,19 @@
 //                             digit place at once (shared-memory bins, then global atomics);
 //   2. radix_scan_hist_kernel exclusive-scans each histogram into bucket bases and marks a digit
 //                             place as skippable when one bucket holds every key;
-//   3. onesweep_kernel        once per non-skipped digit place: a tile of keys is ranked inside
-//                             the CTA (warp ballots, match.any for a third of the keys, per-warp
-//                             counters), the tile's per-digit counts are published, the keys are
-//                             staged in shared memory, then the counts are chained to the
+//   3. onesweep_kernel        once per non-skipped digit place, persistent CTAs (two per SM) that take
+//                             tiles by an atomic ticket: while a tile is processed the next tile's
+//                             keys and values are already being loaded into registers.  A tile is
+//                             ranked inside the CTA on per-warp shared-memory counters -- every lane
+//                             increments its digit's counter, lanes of a warp that collide on a digit
+//                             are ordered by a short ballot loop (about two ballots per 32 keys; a row
+//                             with many collisions falls back to one ballot per digit bit) --, the
+//                             tile's per-digit counts are published, keys and values are staged side
+//                             by side in shared memory in bucket order, the counts are chained to the
 //                             preceding tiles by decoupled look-back (one thread per digit, four
-//                             descriptors fetched per round trip), and keys then values leave
-//                             shared memory so that each bucket's run is written contiguously;
-//                             each CTA also asks L2 for the tile the next wave will take;
+//                             descriptors fetched per round trip, bounded waits), and the pairs leave
+//                             shared memory in one loop so that each bucket's run is written
+//                             contiguously;
 //   4. radix_copy_back_kernel only if an odd number of places ran: moves the result from the
 //                             alternate buffer to the caller's.
 // A pass therefore reads and writes each key (and value) exactly once.  The sort is stable.
@@ -173,7 +178,7 @@ template <int KB, int VB> struct onesweep_tuning {
 // up to 256 bins and where a bin's items go.
 template <class UK, class UV, bool IS_FLOAT> struct radix_pass_policy {
   static constexpr int BITS = RADIX_BITS;       // ballots per key
-  static constexpr int MATCH_EVERY = TB200_SWEEP_MATCH_EVERY;   // every third row is ranked with match.any instead
+  static constexpr int MATCH_EVERY = TB200_SWEEP_MATCH_EVERY;   // n > 0: every n-th row is ranked with match.any instead (0: never)
   UK* dst; UV* vdst; int shift; unsigned dmask;
   __device__ __forceinline__ unsigned digit(UK k) const { return key_digit<IS_FLOAT>(k, shift, dmask); }
   __device__ __forceinline__ UK* keys_of(unsigned) const { return dst; }

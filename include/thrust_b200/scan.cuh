@@ -1,6 +1,8 @@
 // Inclusive / exclusive scan for sm_100a: a single-pass kernel with decoupled look-back (any operator,
-// any iterator, small and medium inputs) and a two-pass "reduce, then scan" route for large inputs
-// (further down).
+// any iterator, small and medium inputs) and, for large inputs with a commutative operator and a
+// contiguous output, one persistent kernel that walks the input in L2-sized windows -- reduce, fold,
+// scan per window, the second read served from L2 (scan_window_kernel, further down; the two-launch
+// "reduce, then scan" route it grew out of remains for -DTB200_SCAN_NO_WINDOW).
 //
 // Single pass:
 // One CTA per tile; tiles are handed out by an atomic ticket so that a tile's predecessors have
