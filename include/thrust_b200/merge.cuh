@@ -287,15 +287,26 @@ block_sort_kernel(KeyIt keys, ValIt vals, KeyOutIt keys_out, ValOutIt vals_out, 
       if (!before(s_key[b0 + d - 1 - mid], s_idx[b0 + d - 1 - mid], s_key[a0 + mid], s_idx[a0 + mid])) lo = mid + 1; else hi = mid;
     }
     unsigned ai = lo, bi = d - lo;
+    // the two candidates stay in registers; only the side that was taken is read again
+    K cand_a = K(), cand_b = K();
+    unsigned short cand_ai = 0, cand_bi = 0;
+    if (ai < len) { cand_a = s_key[a0 + ai]; cand_ai = s_idx[a0 + ai]; }
+    if (bi < len) { cand_b = s_key[b0 + bi]; cand_bi = s_idx[b0 + bi]; }
 #pragma unroll
     for (int i = 0; i < IPT; ++i) {
       bool take_b;
       if (bi >= len) take_b = false;
       else if (ai >= len) take_b = true;
-      else take_b = before(s_key[b0 + bi], s_idx[b0 + bi], s_key[a0 + ai], s_idx[a0 + ai]);
-      const unsigned s = take_b ? b0 + bi : a0 + ai;
-      k[i] = s_key[s]; idx[i] = s_idx[s];
-      if (take_b) ++bi; else ++ai;
+      else take_b = before(cand_b, cand_bi, cand_a, cand_ai);
+      if (take_b) {
+        k[i] = cand_b; idx[i] = cand_bi;
+        ++bi;
+        if (bi < len) { cand_b = s_key[b0 + bi]; cand_bi = s_idx[b0 + bi]; }
+      } else {
+        k[i] = cand_a; idx[i] = cand_ai;
+        ++ai;
+        if (ai < len) { cand_a = s_key[a0 + ai]; cand_ai = s_idx[a0 + ai]; }
+      }
     }
   }
   __syncthreads();
